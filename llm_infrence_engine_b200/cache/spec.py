@@ -12,6 +12,7 @@ class PagedKVSpec:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: all keys are kept; n: only keys p - n < j <= p are ever read
+    v_head_dim: Optional[int] = None  # size of a value row; None: as the keys; 0: no value pool (values are read out of the key rows)
 
 
 @dataclass(frozen=True)

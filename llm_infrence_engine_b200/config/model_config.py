@@ -162,6 +162,9 @@ def read_config_json(folder: str | Path) -> dict:
 
 
 def architecture_name(d: Mapping[str, Any]) -> str:
+    """The model class a config.json names: the first entry of ``architectures``, or a plain ``architecture`` string."""
+    if isinstance(d.get("architecture"), str) and "architectures" not in d:
+        return d["architecture"]
     arch = d.get("architectures")
     if not isinstance(arch, (list, tuple)) or not arch or not isinstance(arch[0], str):
         raise ConfigError("config.json has no 'architectures' list naming the model class")
@@ -170,3 +173,153 @@ def architecture_name(d: Mapping[str, Any]) -> str:
 
 def config_field_names(cls) -> list[str]:
     return [f.name for f in fields(cls)]
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Luvutar: a decoder whose config.json lists its layers one by one.
+
+def _sub(d: Mapping[str, Any], key: str, where: str) -> Mapping[str, Any]:
+    v = d.get(key)
+    if not isinstance(v, Mapping):
+        raise ConfigError(f"config.json: {where}'{key}' must be an object")
+    return v
+
+
+def _pos_int(d: Mapping[str, Any], key: str, where: str) -> int:
+    v = d.get(key)
+    if isinstance(v, bool) or not isinstance(v, int) or v <= 0:
+        raise ConfigError(f"config.json: {where}'{key}' must be a positive integer, got {v!r}")
+    return v
+
+
+def _number(d: Mapping[str, Any], key: str, where: str) -> float:
+    v = d.get(key)
+    if isinstance(v, bool) or not isinstance(v, (int, float)):
+        raise ConfigError(f"config.json: {where}'{key}' must be a number, got {v!r}")
+    return float(v)
+
+
+@dataclass(frozen=True)
+class BiasedAttentionConfig:
+    """Mixer ``attention``: grouped heads without rotation; the position enters through a query temperature and a learned
+    bias by bucketed distance."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    bias_max: Optional[float] = None       # distance from which the bias table's last row is used; None: no bias table
+    temp_coef: float = 0.0                 # query temperature 1 + coef * ln(floor((p + 1) / every) + 1); 0 / 0: none
+    temp_every: int = 0
+    kv_from: Optional[int] = None          # the layer whose keys and values this one reads instead of making its own
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "BiasedAttentionConfig":
+        qt = m.get("q_temp")
+        if qt is not None and not isinstance(qt, Mapping):
+            raise ConfigError(f"config.json: {where}'q_temp' must be an object")
+        kv_from = m.get("kv_from")
+        if kv_from is not None and (isinstance(kv_from, bool) or not isinstance(kv_from, int) or kv_from < 0):
+            raise ConfigError(f"config.json: {where}'kv_from' must be a layer index, got {kv_from!r}")
+        heads, kv_heads = _pos_int(m, "heads", where), _pos_int(m, "kv_heads", where)
+        if heads % kv_heads:
+            raise ConfigError(f"config.json: {where}{heads} heads cannot share {kv_heads} kv_heads")
+        dim = _pos_int(m, "dim", where)
+        return cls(heads, kv_heads, dim, _pos_int(m, "vdim", where) if "vdim" in m else dim, _number(m, "scale", where),
+                   _number(m, "bias_max", where) if m.get("bias_max") is not None else None,
+                   _number(qt, "coef", where + "q_temp.") if qt else 0.0, _pos_int(qt, "every", where + "q_temp.") if qt else 0, kv_from)
+
+
+@dataclass(frozen=True)
+class LatentAttentionConfig:
+    """Mixer ``latent_attention``: queries and keys/values through low-rank latents, one rotated key part for all heads."""
+
+    heads: int
+    dim: int          # unrotated query/key dimensions per head
+    rot_dim: int      # rotated ones
+    vdim: int
+    q_rank: int
+    kv_rank: int
+    scale: float
+    rot_base: float = 10000.0
+    rot_dims: int = 0                # how many of the rot_dim entries turn (0: none)
+    window: Optional[int] = None     # keys a position sees, itself included; None: all
+    sink: bool = True
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "LatentAttentionConfig":
+        rot, mask = m.get("rot"), m.get("mask")
+        for name, v in (("rot", rot), ("mask", mask)):
+            if v is not None and not isinstance(v, Mapping):
+                raise ConfigError(f"config.json: {where}'{name}' must be an object")
+        rot_dim = _pos_int(m, "rot_dim", where)
+        rot_dims = _pos_int(rot, "dims", where + "rot.") if rot else 0
+        if rot_dims % 2 or rot_dims > rot_dim:
+            raise ConfigError(f"config.json: {where}rot.dims {rot_dims} must be even and at most rot_dim {rot_dim}")
+        return cls(_pos_int(m, "heads", where), _pos_int(m, "dim", where), rot_dim, _pos_int(m, "vdim", where), _pos_int(m, "q_rank", where),
+                   _pos_int(m, "kv_rank", where), _number(m, "scale", where), _number(rot, "base", where + "rot.") if rot else 10000.0, rot_dims,
+                   _pos_int(mask, "size", where + "mask.") if mask else None)
+
+
+@dataclass(frozen=True)
+class LuvutarLayerConfig:
+    kind: str                  # "attention" or "latent_attention"
+    mixer: Any
+    ff: Optional[int]          # width of the dense feed-forward, None: the layer has none
+
+
+@dataclass(frozen=True)
+class LuvutarConfig:
+    """The whole of a Luvutar config.json: vocabulary, width, norm epsilon, residual streams and the list of layers."""
+
+    architecture = "Luvutar"
+    MIXERS = {"attention": BiasedAttentionConfig, "latent_attention": LatentAttentionConfig}
+
+    vocab: int
+    width: int
+    eps: float
+    streams: Optional[int]     # None: one residual stream with plain additions; n: hyper-connections over n streams
+    layers: tuple
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "LuvutarConfig":
+        if not isinstance(d.get("layers"), (list, tuple)) or not d["layers"]:
+            raise ConfigError("config.json: 'layers' must be a list with at least one layer")
+        layers = []
+        for i, layer in enumerate(d["layers"]):
+            where = f"layers[{i}]."
+            if not isinstance(layer, Mapping):
+                raise ConfigError(f"config.json: layers[{i}] must be an object")
+            kind = layer.get("type")
+            if kind not in cls.MIXERS:
+                raise ConfigError(f"config.json: {where}type {kind!r} is not one of {sorted(cls.MIXERS)}")
+            mixer = cls.MIXERS[kind].from_dict(_sub(layer, "mixer", where), where + "mixer.")
+            mlp = layer.get("mlp")
+            ff = None
+            if mlp is not None:
+                if not isinstance(mlp, Mapping) or mlp.get("kind", "dense") != "dense":
+                    raise ConfigError(f"config.json: {where}mlp must be null or an object of kind 'dense'")
+                ff = _pos_int(mlp, "ff", where + "mlp.")
+            layers.append(LuvutarLayerConfig(kind, mixer, ff))
+        streams = d.get("streams")
+        cfg = cls(_pos_int(d, "vocab", ""), _pos_int(d, "width", ""), _number(_sub(d, "norm", ""), "eps", "norm."),
+                  _pos_int(d, "streams", "") if streams is not None else None, tuple(layers))
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if not self.eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.eps}")
+        if self.streams is not None and self.streams > 16:
+            raise ConfigError(f"streams {self.streams}: at most 16 residual streams are built")
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            src = getattr(m, "kv_from", None)
+            if src is None:
+                continue
+            if src >= i or self.layers[src].kind != layer.kind or self.layers[src].mixer.kv_from is not None:
+                raise ConfigError(f"layers[{i}].mixer.kv_from {src} must name an earlier layer of the same type with keys and values of its own")
+            o = self.layers[src].mixer
+            if (o.kv_heads, o.dim, o.vdim) != (m.kv_heads, m.dim, m.vdim):
+                raise ConfigError(f"layers[{i}] reads the keys and values of layer {src}, whose head sizes differ")

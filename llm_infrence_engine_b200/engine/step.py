@@ -41,7 +41,7 @@ class PagedKVBinding:
 
     group: int
     k: torch.Tensor  # [num_pages, num_kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    v: Optional[torch.Tensor]  # [num_pages, num_kv_heads, page_size, v_head_dim]; None where values are read out of the key rows
     write: bool = True
 
 
@@ -109,11 +109,11 @@ class ModelRunner:
         specs = spec.cache_specs()
         for entry, cs in enumerate(specs):
             if isinstance(cs, PagedKVSpec):
-                shape = (num_pages, cs.num_kv_heads, page_size, cs.head_dim)
-                k = torch.zeros(shape, dtype=dtype, device=self.device)
-                v = torch.zeros(shape, dtype=dtype, device=self.device)
+                v_dim = cs.head_dim if cs.v_head_dim is None else cs.v_head_dim
+                k = torch.zeros((num_pages, cs.num_kv_heads, page_size, cs.head_dim), dtype=dtype, device=self.device)
+                v = torch.zeros((num_pages, cs.num_kv_heads, page_size, v_dim), dtype=dtype, device=self.device) if v_dim else None
                 self.bindings.append(PagedKVBinding(group_of_entry[entry], k, v))
-                self.kv_bytes_per_token += 2 * cs.num_kv_heads * cs.head_dim * k.element_size()
+                self.kv_bytes_per_token += cs.num_kv_heads * (cs.head_dim + v_dim) * k.element_size()
             elif isinstance(cs, FixedStateSpec):
                 self.bindings.append(StateBinding(torch.zeros((max_seqs + 1,) + tuple(cs.shape), dtype=torch.float32, device=self.device)))
             elif cs is None:
@@ -386,6 +386,8 @@ class ModelRunner:
             if isinstance(b, StateBinding):
                 self.K.zero_fresh_state(b.state, ctx.seq_slots, ctx.seq_starts_dev, ctx.positions)
         residual = spec.embedding.forward(ctx)
+        if spec.streams is not None:   # several residual streams: the layers work on [N, streams, hidden]
+            residual = spec.streams.expand(ctx, residual)
         for call in spec.schedule:
             b = self.bindings[call.cache]
             if b is not None and b.write != call.write:
@@ -395,7 +397,10 @@ class ModelRunner:
             if hasattr(self.K, "flush"):
                 self.K.flush()  # nothing reads the residual stream any more: an addition that was put off must not stay behind
             return None
-        h = spec.final_norm.norm_rows(ctx, residual, logit_rows)
+        if spec.streams is not None:
+            h = spec.streams.norm_rows(ctx, spec.final_norm, residual, logit_rows)
+        else:
+            h = spec.final_norm.norm_rows(ctx, residual, logit_rows)
         return spec.head.forward(ctx, h)
 
     # ------------------------------------------------------------------ accounting

@@ -30,10 +30,11 @@ class ModelSpec:
     schedule: List[LayerCall]
     final_norm: Norm
     head: OutputHead
+    streams: Any = None             # None: one residual stream [N, hidden]; else a part with expand(ctx, x) and norm_rows(ctx, norm, xs, rows)
 
     def parts(self) -> List[Part]:
         out: List[Part] = []
-        for top in [self.embedding, *self.layers, self.final_norm, self.head]:
+        for top in [self.embedding, *self.layers, self.final_norm, self.head, *([self.streams] if self.streams is not None else [])]:
             out.extend(walk(top))
         return out
 

@@ -32,6 +32,12 @@ TABLE = "table"    # integers, kept as int32
 # How the random-weights mode draws a checkpoint tensor.
 INIT_NORMAL = "normal"      # N(0, 0.02): matrices, embeddings and biases
 INIT_NORM = "norm_weight"   # 1 + U(-0.1, 0.1): weights of norms
+INIT_SMALL = "small"        # N(0, 0.1): weights kept around zero, biases by distance, sinks
+INIT_SHARE = "share"        # 1 / n + N(0, 0.05) for a vector of n: how much of each residual stream a sublayer reads
+INIT_ONES = "ones"          # 1 + N(0, 0.05): how much of a sublayer's result each residual stream takes
+INIT_EYE = "eye"            # identity + N(0, 0.05): how the residual streams mix
+
+ANY = -1  # a dimension of a Source's shape that the checkpoint decides (the part reads it off the tensor it is given)
 
 
 @dataclass(frozen=True)
@@ -42,6 +48,10 @@ class Source:
     shape: Tuple[int, ...]
     init: str = INIT_NORMAL
     optional: bool = False  # may be absent (for instance the output head of a tied checkpoint)
+    free: int = 0           # the size that random weights give to a dimension the checkpoint decides (``ANY``)
+
+    def drawn_shape(self) -> Tuple[int, ...]:
+        return tuple(self.free if n == ANY else n for n in self.shape)
 
 
 @dataclass(frozen=True)

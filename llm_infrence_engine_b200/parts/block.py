@@ -18,15 +18,18 @@ class PreNormBlock(Part):
 
     graph_safe = True
 
-    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Norm, ff: FeedForward):
+    def __init__(self, norm1: Norm, mixer: Mixer, norm2: Optional[Norm] = None, ff: Optional[FeedForward] = None):
+        if (norm2 is None) != (ff is None):
+            raise ValueError("a feed-forward comes with its norm, or neither is there")
         self.norm1, self.mixer, self.norm2, self.ff = norm1, mixer, norm2, ff
 
     def children(self) -> Sequence[Part]:
-        return (self.norm1, self.mixer, self.norm2, self.ff)
+        return tuple(p for p in (self.norm1, self.mixer, self.norm2, self.ff) if p is not None)
 
     def cache_spec(self):
         return self.mixer.cache_spec()
 
     def forward(self, ctx, residual: torch.Tensor, cache) -> None:
         self.mixer.forward(ctx, self.norm1.norm(ctx, residual), cache, residual)
-        self.ff.forward(ctx, self.norm2.norm(ctx, residual), residual)
+        if self.ff is not None:   # a layer may be a mixer alone
+            self.ff.forward(ctx, self.norm2.norm(ctx, residual), residual)

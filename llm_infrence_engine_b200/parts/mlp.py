@@ -37,3 +37,26 @@ class GatedMLP(FeedForward):
     def forward(self, ctx, h, residual):
         K = ctx.K
         K.linear(K.gate_up_act(h, self.w_gate_up, ctx.dtype), self.w_down, add_to=residual)
+
+
+class DenseMLP(FeedForward):
+    """``down(act(up(x)))`` without biases; ``act`` is the tanh form of GELU,
+    ``0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``, computed in 32-bit on the product's sums."""
+
+    graph_safe = True
+    ACTIVATIONS = ("gelu_tanh",)
+
+    def __init__(self, hidden: int, intermediate: int, up_name: str, down_name: str, activation: str = "gelu_tanh"):
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"activation '{activation}' is not one of {self.ACTIVATIONS}")
+        self.hidden, self.intermediate, self.up_name, self.down_name, self.activation = hidden, intermediate, up_name, down_name, activation
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {"w_up": ParamSpec((Source(self.up_name, (self.intermediate, self.hidden)),), MATRIX),
+                "w_down": ParamSpec((Source(self.down_name, (self.hidden, self.intermediate)),), MATRIX)}
+
+    def forward(self, ctx, h, residual):
+        K = ctx.K
+        K.linear(K.linear_act(h, self.w_up, self.activation, ctx.dtype), self.w_down, add_to=residual)

@@ -5,7 +5,7 @@ from typing import Dict, Optional
 
 import torch
 
-from .base import INIT_NORM, VECTOR, Norm, ParamSpec, Source
+from .base import INIT_NORM, INIT_SMALL, VECTOR, Norm, ParamSpec, Source
 
 
 class RMSNorm(Norm):
@@ -13,18 +13,32 @@ class RMSNorm(Norm):
 
     The reference reduces in 32-bit, casts to the model's dtype and multiplies by the weight there
     (src/miniserve/model.py:69-73). ``eps`` sits inside the square root, added to the mean.
+
+    ``offset``: what is added to the stored weight before it is used. A checkpoint that keeps its norm weights around zero
+    (the scaling is ``1 + w``) has ``offset = 1``; the sum is made once, in 32-bit, when the weights are bound.
+
+    ``norm_streams``: the norm of a weighted sum of several residual streams ``[N, streams, dim]``, everything in 32-bit up
+    to the one rounding of the result (the kernel also carries out a stream update that was put off until now).
     """
 
     graph_safe = True
 
-    def __init__(self, dim: int, eps: float, weight_name: str):
+    def __init__(self, dim: int, eps: float, weight_name: str, offset: float = 0.0):
         self.dim = dim
         self.eps = float(eps)
         self.weight_name = weight_name
+        self.offset = float(offset)
         self.weight: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
-        return {"weight": ParamSpec((Source(self.weight_name, (self.dim,), INIT_NORM),), VECTOR)}
+        init = INIT_NORM if self.offset == 0.0 else INIT_SMALL
+        return {"weight": ParamSpec((Source(self.weight_name, (self.dim,), init),), VECTOR)}
+
+    def bind(self, tensors) -> None:
+        self.weight = tensors["weight"] + self.offset if self.offset else tensors["weight"]
+
+    def norm_streams(self, ctx, streams, coef, rows=None):
+        return ctx.K.streams_norm(streams, coef, self.weight, self.eps, ctx.dtype, rows)
 
     def norm(self, ctx, residual):
         return ctx.K.add_rmsnorm(residual, None, self.weight, self.eps, ctx.dtype)

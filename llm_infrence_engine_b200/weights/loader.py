@@ -19,7 +19,7 @@ from typing import Dict, List, Tuple
 import torch
 
 from ..models.spec import ModelSpec
-from ..parts.base import MATRIX, TABLE, VECTOR, ParamSpec, Part
+from ..parts.base import ANY, MATRIX, TABLE, VECTOR, ParamSpec, Part
 from .safetensors_io import SafetensorsFile
 
 _FLOATS = (torch.float32, torch.bfloat16, torch.float16, torch.float64)
@@ -83,7 +83,7 @@ def load_weights(spec: ModelSpec, folder: str | Path, dtype: torch.dtype, device
             if name not in where:
                 continue
             got_dtype, got_shape = where[name].info(name)
-            if tuple(got_shape) != tuple(shape):
+            if len(got_shape) != len(shape) or any(w != ANY and g != w for g, w in zip(got_shape, shape)):
                 wrong_shape.append((name, got_shape, shape))
             if kind == TABLE and got_dtype not in _INTS:
                 wrong_dtype.append((name, got_dtype, "an integer type"))

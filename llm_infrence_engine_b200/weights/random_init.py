@@ -14,7 +14,7 @@ from typing import Any, Dict, Mapping
 import torch
 
 from ..models.registry import build_model_spec
-from ..parts.base import INIT_NORM, INIT_NORMAL
+from ..parts.base import INIT_EYE, INIT_NORM, INIT_NORMAL, INIT_ONES, INIT_SHARE, INIT_SMALL
 from .safetensors_io import write_safetensors_stream
 
 _STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
@@ -33,10 +33,19 @@ def _sources(config_json: Mapping[str, Any]):
 
 
 def _draw(s, gen: torch.Generator, std: float) -> torch.Tensor:
+    shape = s.drawn_shape()
     if s.init == INIT_NORM:
-        return 1.0 + (torch.rand(s.shape, generator=gen) * 0.2 - 0.1)
+        return 1.0 + (torch.rand(shape, generator=gen) * 0.2 - 0.1)
     if s.init == INIT_NORMAL:
-        return torch.randn(s.shape, generator=gen) * std
+        return torch.randn(shape, generator=gen) * std
+    if s.init == INIT_SMALL:
+        return torch.randn(shape, generator=gen) * 0.1
+    if s.init == INIT_SHARE:
+        return 1.0 / shape[-1] + torch.randn(shape, generator=gen) * 0.05
+    if s.init == INIT_ONES:
+        return 1.0 + torch.randn(shape, generator=gen) * 0.05
+    if s.init == INIT_EYE:
+        return torch.eye(shape[-1]) + torch.randn(shape, generator=gen) * 0.05
     raise ValueError(f"tensor '{s.name}' asks for unknown initialisation '{s.init}'")
 
 
@@ -58,7 +67,7 @@ def write_random_model(config_json: Mapping[str, Any], folder: str | Path, seed:
     sources = list(_sources(config_json))
     by_name = {s.name: s for s in sources}
     gen = torch.Generator().manual_seed(int(seed))
-    write_safetensors_stream(folder / "model.safetensors", [(s.name, dtype, tuple(s.shape)) for s in sources],
+    write_safetensors_stream(folder / "model.safetensors", [(s.name, dtype, s.drawn_shape()) for s in sources],
                              lambda name: _draw(by_name[name], gen, std).to(dtype))
     cfg = dict(config_json)
     cfg["torch_dtype"] = store_dtype

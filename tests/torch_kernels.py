@@ -120,6 +120,116 @@ class TorchKernels:
         g, u = gu[:, :i].float(), gu[:, i:].float()
         return (g * torch.sigmoid(g) * u).to(gu.dtype)
 
+    # ------------------------------------------------------------------ several residual streams
+    def zeros_like_rows(self, streams):
+        return torch.zeros(streams.shape[0], streams.shape[-1], dtype=torch.float32)
+
+    def streams_expand(self, x, streams):
+        return x[:, None, :].repeat(1, streams, 1).contiguous()
+
+    def streams_update(self, streams, y, mix, coef_out):
+        new = torch.einsum("st,nsh->nth", mix.float(), streams) + coef_out.float()[None, :, None] * y.float()[:, None, :]
+        streams.copy_(new)
+
+    def streams_norm(self, streams, coef_in, weight, eps, out_dtype, rows=None):
+        x = streams if rows is None else streams[rows.long()]
+        u = torch.einsum("s,nsh->nh", coef_in.float(), x)
+        return (u * torch.rsqrt(u.pow(2).mean(-1, keepdim=True) + eps) * weight.float()).to(out_dtype)
+
+    def flush(self):
+        pass
+
+    # ------------------------------------------------------------------ feed-forward with one product going in
+    def linear_act(self, x, w, activation, out_dtype=None):
+        z = x.float() @ w.float().T
+        if activation != "gelu_tanh":
+            raise ValueError(activation)
+        y = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+        return y.to(out_dtype or x.dtype)
+
+    # ------------------------------------------------------------------ attention with extras
+    def kv_store(self, z, k_col, v_col, slot_mapping, k_pool, v_pool, num_kv_heads, head_dim, v_head_dim, page_size):
+        N = z.shape[0]
+        page, off = (slot_mapping // page_size).long(), (slot_mapping % page_size).long()
+        k_pool[page, :, off] = z[:, k_col:k_col + num_kv_heads * head_dim].reshape(N, num_kv_heads, head_dim).to(k_pool.dtype)
+        v_pool[page, :, off] = z[:, v_col:v_col + num_kv_heads * v_head_dim].reshape(N, num_kv_heads, v_head_dim).to(v_pool.dtype)
+
+    def attention_ext(self, q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions,
+                      page_size, scale, window, max_context, temp=(0.0, 0), rel=None, rel_rows=None, sink=None, gate=None, gate_col=0,
+                      gate_per_head=False, batch=None, num_splits=None):
+        N = q.shape[0]
+        rep = num_heads // num_kv_heads
+        qs = q[:, q_col:q_col + num_heads * head_dim].float().view(N, num_heads, head_dim)
+        out = torch.zeros(N, num_heads, v_head_dim)
+        for t in range(N):
+            p = int(positions[t])
+            lo = 0 if not window else max(0, p - window + 1)
+            keys = torch.arange(lo, p + 1)
+            pages = block_table[int(token_seq[t])][(keys // page_size)].long()
+            offs = (keys % page_size).long()
+            k = k_pool[pages, :, offs].float()                                   # [S, kv heads, head_dim]
+            v = v_pool[pages, :, offs].float() if v_pool is not None else k[..., :v_head_dim]
+            factor = scale
+            if temp[1]:
+                factor = scale * (1.0 + temp[0] * math.log((p + 1) // temp[1] + 1))
+            for h in range(num_heads):
+                s = (k[:, h // rep] @ qs[t, h]) * factor
+                if rel is not None:
+                    dist = p - keys
+                    row = torch.where(dist < rel_rows.shape[0], rel_rows.long()[dist.clamp(max=rel_rows.shape[0] - 1)], rel.shape[0] - 1)
+                    s = s + rel[row, h].float()
+                if sink is not None:
+                    top = max(float(s.max()), float(sink[h]))
+                    e = torch.exp(s - top)
+                    pr = e / (e.sum() + math.exp(float(sink[h]) - top))
+                else:
+                    pr = torch.softmax(s, dim=0)
+                out[t, h] = pr @ v[:, h // rep]
+        if gate is not None:
+            if gate_per_head:
+                out = out * torch.sigmoid(gate[:, gate_col:gate_col + num_heads].float())[:, :, None]
+            else:
+                out = out * torch.sigmoid(gate[:, gate_col:gate_col + num_heads * v_head_dim].float()).view(N, num_heads, v_head_dim)
+        return out.reshape(N, num_heads * v_head_dim).to(q.dtype)
+
+    # ------------------------------------------------------------------ latent attention
+    @staticmethod
+    def _turn_pairs(x, cos, sin, dims):
+        """Neighbouring pairs (2i, 2i+1) of the first ``dims`` entries of the last axis; cos/sin [N, dims/2] broadcast over the middle axes."""
+        if not dims:
+            return x
+        shape = [x.shape[0]] + [1] * (x.dim() - 2) + [dims // 2]
+        c, s = cos.view(shape), sin.view(shape)
+        u, v = x[..., 0:dims:2], x[..., 1:dims:2]
+        out = x.clone()
+        out[..., 0:dims:2] = u * c - v * s
+        out[..., 1:dims:2] = v * c + u * s
+        return out
+
+    def latent_prepare(self, z, q_rank, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, eps, cos, sin, slot_mapping, kc_pool, page_size, write=True):
+        zf = z.float()
+        dq, c, r = zf[:, :q_rank], zf[:, q_rank:q_rank + kv_rank], zf[:, q_rank + kv_rank:q_rank + kv_rank + rot_dim]
+        cq = dq * torch.rsqrt(dq.pow(2).mean(-1, keepdim=True) + eps) * q_norm.float()
+        if write:
+            c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * kv_norm.float()
+            r = self._turn_pairs(r, cos, sin, rot_dims)
+            page, off = (slot_mapping // page_size).long(), (slot_mapping % page_size).long()
+            kc_pool[page, 0, off] = torch.cat([c, r], dim=-1).to(kc_pool.dtype)
+        return cq.to(z.dtype)
+
+    def latent_absorb(self, q, w_uk, cos, sin, num_heads, head_dim, rot_dim, rot_dims, kv_rank):
+        N = q.shape[0]
+        qf = q.float().view(N, num_heads, head_dim + rot_dim)
+        flat = torch.einsum("nhd,hdr->nhr", qf[..., :head_dim], w_uk.float().view(num_heads, head_dim, kv_rank))
+        turned = self._turn_pairs(qf[..., head_dim:], cos, sin, rot_dims)
+        return torch.cat([flat, turned], dim=-1).reshape(N, -1).to(q.dtype)
+
+    def latent_expand(self, o_lat, w_uv, gate, gate_col, num_heads, kv_rank, v_head_dim):
+        N = o_lat.shape[0]
+        o = torch.einsum("nhr,hvr->nhv", o_lat.float().view(N, num_heads, kv_rank), w_uv.float().view(num_heads, v_head_dim, kv_rank))
+        o = o.reshape(N, -1) * torch.sigmoid(gate[:, gate_col:gate_col + num_heads * v_head_dim].float())
+        return o.to(o_lat.dtype)
+
     def argmax(self, logits):
         return logits.argmax(-1).to(torch.int32)
 
