@@ -455,3 +455,59 @@ LLMIE_API int llmie_add_into(float* residual, const void* delta, long long total
     }
     return launch_status();
 }
+
+// ------------------------------------------------------------------------------------------------
+// Keys and values of a fused projection into their pages: z[n] holds nkv key heads of dk entries from column k_col and nkv
+// value heads of dv entries from column v_col; pools are [page][kv head][offset][d], slot = page * page_size + offset.
+template <typename T>
+__global__ void kv_store_kernel(const T* __restrict__ z, int z_stride, int k_col, int v_col, const int* __restrict__ slots,
+                                T* __restrict__ k_pool, T* __restrict__ v_pool, int nkv, int dk, int dv, int page_size) {
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x;
+    const int slot = slots[n];
+    const int page = slot / page_size, off = slot % page_size;
+    const T* row = z + (size_t)n * z_stride;
+    for (int i = threadIdx.x; i < nkv * dk; i += blockDim.x) {
+        const int h = i / dk, c = i % dk;
+        k_pool[(((size_t)page * nkv + h) * page_size + off) * dk + c] = row[k_col + i];
+    }
+    for (int i = threadIdx.x; i < nkv * dv; i += blockDim.x) {
+        const int h = i / dv, c = i % dv;
+        v_pool[(((size_t)page * nkv + h) * page_size + off) * dv + c] = row[v_col + i];
+    }
+}
+
+LLMIE_API int llmie_kv_store(const void* z, int z_stride, int k_col, int v_col, const int* slots, void* k_pool, void* v_pool, int N, int nkv,
+                             int dk, int dv, int page_size, int dtype, cudaStream_t s) {
+    if (N <= 0) return 0;
+    if (nkv < 1 || dk < 1 || dv < 1 || page_size < 1 || !slots || !k_pool || !v_pool) return LLMIE_ERR_BAD_ARGUMENT;
+    if (dtype == DT_F32)
+        return launch_kernel(kv_store_kernel<float>, dim3(N), dim3(128), 0, s, (const float*)z, z_stride, k_col, v_col, slots, (float*)k_pool, (float*)v_pool, nkv, dk, dv, page_size);
+    return launch_kernel(kv_store_kernel<bf16>, dim3(N), dim3(128), 0, s, (const bf16*)z, z_stride, k_col, v_col, slots, (bf16*)k_pool, (bf16*)v_pool, nkv, dk, dv, page_size);
+}
+
+// ------------------------------------------------------------------------------------------------
+// out = act(in), elementwise in 32-bit. kind 0: the tanh form of GELU, 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+// With `clear_in` the input is set to zero after it was read (a float32 accumulation buffer of a split-K product).
+template <typename TI, typename TO>
+__global__ void act_kernel(TI* __restrict__ in, TO* __restrict__ out, long long total, int kind, int clear_in) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float z = to_f32(in[i]);
+    if (clear_in) in[i] = from_f32<TI>(0.f);
+    const float y = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    out[i] = from_f32<TO>(y);
+}
+
+LLMIE_API int llmie_act(void* in, void* out, long long total, int kind, int clear_in, int in_dtype, int out_dtype, cudaStream_t s) {
+    if (total <= 0) return 0;
+    if (kind != 0) return LLMIE_ERR_BAD_ARGUMENT;
+    const dim3 grid((unsigned)((total + 255) / 256));
+    if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_kernel(act_kernel<float, float>, grid, dim3(256), 0, s, (float*)in, (float*)out, total, kind, clear_in);
+    if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_kernel(act_kernel<float, bf16>, grid, dim3(256), 0, s, (float*)in, (bf16*)out, total, kind, clear_in);
+    if (in_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_kernel(act_kernel<bf16, bf16>, grid, dim3(256), 0, s, (bf16*)in, (bf16*)out, total, kind, clear_in);
+    return LLMIE_ERR_BAD_ARGUMENT;
+}

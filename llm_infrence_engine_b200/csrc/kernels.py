@@ -68,6 +68,10 @@ class CudaKernels:
         # A library product that is to be added into the residual stream is kept here until the next kernel that reads
         # the stream: that kernel is usually the norm, which adds and normalises in one pass (see ``flush``).
         self._pending_add: Optional[tuple] = None
+        # An update of several residual streams waits here for the norm of the next sublayer, which updates, sums and
+        # normalises in one pass: (streams, the sublayer's result, mix, out coefficients)
+        self._pending_streams: Optional[tuple] = None
+        self._fresh_zero: Optional[torch.Tensor] = None   # the zeroed tensor that ``zeros_like_rows`` handed out last
         self._error_flag: Optional[torch.Tensor] = None
         self._acc_qkv: Optional[torch.Tensor] = None   # float32 sums of a decode step's q/k/v product, read by the attention kernel
         self._dirty_qkv: Optional[torch.Tensor] = None  # those sums while they still wait to be cleared
@@ -80,7 +84,9 @@ class CudaKernels:
         self.last_attention_plan = (1, False)   # (key slices, merged as a cluster) of the last tensor-core attention launch
         self._decode_four_warps = False         # the last decode plan asked for blocks of four warps
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_zero_fresh_state", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
-                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample"):
+                   "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample",
+                   "llmie_streams_expand", "llmie_streams_update", "llmie_streams_norm", "llmie_latent_prepare", "llmie_head_matmul",
+                   "llmie_kv_store", "llmie_act", "llmie_paged_attention_ext_f32", "llmie_paged_attention_ext_bf16"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = None
@@ -107,6 +113,8 @@ class CudaKernels:
         """After an exception in the middle of a step: nothing of it may reach the next one. An addition that was put off
         is dropped, and the accumulation buffers, which every product assumes to be zero, are cleared."""
         self._pending_add = None
+        self._pending_streams = None
+        self._fresh_zero = None
         self._dirty_qkv = None
         for t in [self._acc, self._acc_qkv, *self._retired_acc]:
             if t is not None:
@@ -210,13 +218,16 @@ class CudaKernels:
     def flush(self, residual=None) -> None:
         """Carry out an addition into the residual stream that ``linear(add_to=...)`` has put off. Every method of this
         class that reads or writes the stream does this itself; code that reads the stream's tensor directly calls it first."""
-        if self._pending_add is None:
-            return
-        target, y = self._pending_add
-        if residual is not None and target.data_ptr() != residual.data_ptr():
-            residual = None  # another tensor is wanted: the pending one is finished all the same, nothing may stay behind
-        self._pending_add = None
-        self._check(self.lib.llmie_add_into(_ptr(target), _ptr(y), target.numel(), self._dt(y, "delta"), self._stream()), "add_into")
+        if self._pending_add is not None:
+            target, y = self._pending_add
+            self._pending_add = None
+            self._check(self.lib.llmie_add_into(_ptr(target), _ptr(y), target.numel(), self._dt(y, "delta"), self._stream()), "add_into")
+        if self._pending_streams is not None:
+            xs, y, mix, coef_out = self._pending_streams
+            self._pending_streams = None
+            N, S, H = xs.shape
+            self._check(self.lib.llmie_streams_update(_ptr(xs), _ptr(y), self._dt(y, "y"), _ptr(mix), _ptr(coef_out), N, S, H, self._stream()),
+                        "streams_update")
 
     def _take_pending(self, residual, out_dtype):
         """The put-off addend for ``residual`` if there is one that the norm kernel can add on its way (same dtype as its output)."""
@@ -711,6 +722,219 @@ class CudaKernels:
         self._check(self.lib.llmie_silu_mul(_ptr(gu), _ptr(out), N, I, int(self._is_transient(gu)), self._dt(gu, "gate_up"),
                                             self._dt(out, "out"), _ptr(dirty), ctypes.c_longlong(0 if dirty is None else dirty.numel()),
                                             self._stream()), "silu_mul")
+        return out
+
+    # ------------------------------------------------------------------ several residual streams
+    def zeros_like_rows(self, streams):
+        """A zeroed float32 ``[N, hidden]`` for a sublayer to add its result into (``streams`` is ``[N, S, hidden]``)."""
+        self._fresh_zero = torch.zeros((streams.shape[0], streams.shape[-1]), dtype=torch.float32, device=streams.device)
+        self.launches += 1
+        return self._fresh_zero
+
+    def streams_expand(self, x, streams: int):
+        self.flush()
+        self._need(x, "x", torch.float32, 2)
+        N, H = x.shape
+        xs = torch.empty((N, streams, H), dtype=torch.float32, device=x.device)
+        self._check(self.lib.llmie_streams_expand(_ptr(x), _ptr(xs), N, streams, H, self._stream()), "streams_expand")
+        return xs
+
+    def _check_streams(self, xs, mix, coef_out, what):
+        self._need(xs, "streams", torch.float32, 3)
+        S = xs.shape[1]
+        if S > 16:
+            raise KernelError(f"{what}: at most 16 streams, got {S}")
+        if mix is not None:
+            self._need(mix, "mix", torch.float32, 2)
+            self._need(coef_out, "coef_out", torch.float32, 1)
+            if tuple(mix.shape) != (S, S) or coef_out.shape[0] != S:
+                raise KernelError(f"{what}: mix must be [{S}, {S}] and coef_out [{S}]")
+
+    def streams_update(self, xs, y, mix, coef_out):
+        """``xs[:, t] <- sum_s mix[s, t] xs[:, s] + coef_out[t] y``. Put off until the next ``streams_norm`` of the same
+        streams (one pass does both) or until ``flush``. If ``y`` is the zeroed tensor of ``zeros_like_rows`` and all it
+        holds is a library product that still waits to be added, the product itself is the update and ``y`` is never written."""
+        self._check_streams(xs, mix, coef_out, "streams_update")
+        if self._pending_add is not None and self._pending_add[0] is y and self._fresh_zero is y:
+            y = self._pending_add[1]
+            self._pending_add = None
+        self.flush()
+        self._fresh_zero = None
+        self._need(y, "y", None, 2)
+        if tuple(y.shape) != (xs.shape[0], xs.shape[2]):
+            raise KernelError(f"streams_update: y is {list(y.shape)}, the streams are {list(xs.shape)}")
+        self._dt(y, "y")
+        self._pending_streams = (xs, y, mix, coef_out)
+
+    def streams_norm(self, xs, coef_in, weight, eps, out_dtype, rows=None):
+        """``norm(sum_s coef_in[s] xs[:, s]) * weight`` in ``out_dtype``, of all tokens or of ``rows``; an update of these
+        streams that was put off happens in the same kernel (with ``rows`` it is computed for them and not stored)."""
+        self._check_streams(xs, None, None, "streams_norm")
+        N, S, H = xs.shape
+        self._need(coef_in, "coef_in", torch.float32, 1)
+        self._need(weight, "weight", torch.float32, 1)
+        if coef_in.shape[0] != S or weight.shape[0] != H:
+            raise KernelError(f"streams_norm: coef_in must be [{S}] and weight [{H}]")
+        y = mix = coef_out = None
+        if self._pending_streams is not None and self._pending_streams[0] is xs and self._pending_add is None:
+            _, y, mix, coef_out = self._pending_streams
+            self._pending_streams = None
+        else:
+            self.flush()
+        if rows is not None:
+            self._need(rows, "rows", torch.int32, 1)
+        n_out = N if rows is None else rows.shape[0]
+        out = torch.empty((n_out, H), dtype=out_dtype, device=xs.device)
+        self._check(self.lib.llmie_streams_norm(_ptr(xs), _ptr(y), 0 if y is None else self._dt(y, "y"), _ptr(mix), _ptr(coef_out), _ptr(coef_in),
+                                                _ptr(weight), _ptr(out), _DT[out_dtype], _ptr(rows), n_out, S, H, ctypes.c_float(eps),
+                                                self._stream()), "streams_norm")
+        return out
+
+    # ------------------------------------------------------------------ a product with an activation behind it
+    def linear_act(self, x, w, activation, out_dtype=None):
+        """``act(x w^T)``; the activation is computed in 32-bit on the product's sums where those are at hand (small batches)."""
+        if activation != "gelu_tanh":
+            raise KernelError(f"linear_act: activation '{activation}' is not built")
+        out_dtype = out_dtype or x.dtype
+        z = self.linear(x, w, transient=True)
+        clear = self._is_transient(z)
+        out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+        self._check(self.lib.llmie_act(_ptr(z), _ptr(out), ctypes.c_longlong(z.numel()), 0, int(clear), self._dt(z, "z"), _DT[out_dtype],
+                                       self._stream()), "act")
+        return out
+
+    # ------------------------------------------------------------------ attention with extras
+    def kv_store(self, z, k_col, v_col, slot_mapping, k_pool, v_pool, num_kv_heads, head_dim, v_head_dim, page_size):
+        """Keys (``num_kv_heads * head_dim`` columns of ``z`` from ``k_col``) and values (from ``v_col``) into the tokens' cache slots."""
+        self._need(z, "z", None, 2)
+        self._need(slot_mapping, "slot_mapping", torch.int32, 1)
+        for name, pool, d in (("k_pool", k_pool, head_dim), ("v_pool", v_pool, v_head_dim)):
+            self._need(pool, name, z.dtype, 4)
+            if tuple(pool.shape[1:]) != (num_kv_heads, page_size, d):
+                raise KernelError(f"kv_store: {name} is {list(pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {d}]")
+        if max(k_col + num_kv_heads * head_dim, v_col + num_kv_heads * v_head_dim) > z.shape[1]:
+            raise KernelError("kv_store: the key or value columns lie outside the rows")
+        self._check(self.lib.llmie_kv_store(_ptr(z), z.shape[1], k_col, v_col, _ptr(slot_mapping), _ptr(k_pool), _ptr(v_pool), z.shape[0],
+                                            num_kv_heads, head_dim, v_head_dim, page_size, self._dt(z, "z"), self._stream()), "kv_store")
+
+    def attention_ext(self, q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions,
+                      page_size, scale, window, max_context, temp=(0.0, 0), rel=None, rel_rows=None, sink=None, gate=None, gate_col=0,
+                      gate_per_head=False, batch=None, num_splits=None):
+        """Paged attention with extras: the query heads are columns ``q_col ..`` of ``q``; ``v_pool=None`` reads the values out
+        of the key rows (their first ``v_head_dim`` entries); ``temp=(coef, every)`` a query temperature by position;
+        ``rel [rows, heads]`` with ``rel_rows`` (distance -> row) a bias by distance; ``sink [heads]`` joins the denominator;
+        ``gate`` (columns from ``gate_col`` of a tensor with the tokens' rows) an output gate per head or per element."""
+        self._need(q, "q", None, 2)
+        dt = self._dt(q, "q")
+        N = q.shape[0]
+        if num_heads % num_kv_heads:
+            raise KernelError("attention_ext: the query heads must be a multiple of the key/value heads")
+        if q_col + num_heads * head_dim > q.shape[1]:
+            raise KernelError("attention_ext: the rows are too short for the query heads")
+        self._need(k_pool, "k_pool", q.dtype, 4)
+        if tuple(k_pool.shape[1:]) != (num_kv_heads, page_size, head_dim):
+            raise KernelError(f"attention_ext: k_pool is {list(k_pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {head_dim}]")
+        if v_pool is not None:
+            self._need(v_pool, "v_pool", q.dtype, 4)
+            if tuple(v_pool.shape[1:]) != (num_kv_heads, page_size, v_head_dim):
+                raise KernelError(f"attention_ext: v_pool is {list(v_pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {v_head_dim}]")
+        elif v_head_dim > head_dim:
+            raise KernelError("attention_ext: values read out of the key rows cannot be longer than the keys")
+        self._need(block_table, "block_table", torch.int32, 2)
+        self._need(token_seq, "token_seq", torch.int32, 1)
+        self._need(positions, "positions", torch.int32, 1)
+        if block_table.shape[1] * page_size < max_context:
+            raise KernelError(f"attention_ext: block tables of {block_table.shape[1]} pages cannot hold {max_context} tokens")
+        if rel is not None:
+            self._need(rel, "rel", torch.float32, 2)
+            self._need(rel_rows, "rel_rows", torch.int32, 1)
+            if rel.shape[1] != num_heads:
+                raise KernelError("attention_ext: rel needs one column per head")
+        if sink is not None:
+            self._need(sink, "sink", torch.float32, 1)
+            if sink.shape[0] != num_heads:
+                raise KernelError("attention_ext: sink needs one number per head")
+        gate_mode = 0
+        if gate is not None:
+            self._need(gate, "gate", q.dtype, 2)
+            gate_mode = 1 if gate_per_head else 2
+            if gate.shape[0] != N or gate_col + (num_heads if gate_per_head else num_heads * v_head_dim) > gate.shape[1]:
+                raise KernelError("attention_ext: the gate columns lie outside the rows")
+        out = torch.empty((N, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
+        slice_keys = 0 if num_splits else self.slice_keys
+        splits = num_splits or self.attention_slices(max_context)
+        scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
+        esize = q.element_size()
+        fn = self.lib.llmie_paged_attention_ext_f32 if dt == 0 else self.lib.llmie_paged_attention_ext_bf16
+        self._check(fn(ctypes.c_void_p(q.data_ptr() + q_col * esize), q.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
+                       block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads,
+                       head_dim, v_head_dim, page_size, ctypes.c_float(scale), int(window), splits, slice_keys,
+                       ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel), _ptr(rel_rows), 0 if rel_rows is None else rel_rows.shape[0],
+                       0 if rel is None else rel.shape[0], _ptr(sink),
+                       ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1],
+                       gate_mode, self._stream()), "attention_ext")
+        if splits > 1:
+            self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------ latent attention
+    def latent_prepare(self, z, q_rank, kv_rank, rot_dim, rot_dims, q_norm, kv_norm, eps, cos, sin, slot_mapping, kc_pool, page_size, write=True):
+        """From ``z = [query latent | key/value latent | rotated part | ...]``: returns the normed query latent and, with
+        ``write``, puts ``[normed key/value latent | turned rotated part]`` into the tokens' cache rows (one key/value head)."""
+        self._need(z, "z", None, 2)
+        N = z.shape[0]
+        if z.shape[1] < q_rank + kv_rank + rot_dim:
+            raise KernelError("latent_prepare: the rows are too short for the three parts")
+        self._need(q_norm, "q_norm", torch.float32, 1)
+        self._need(kv_norm, "kv_norm", torch.float32, 1)
+        if q_norm.shape[0] != q_rank or kv_norm.shape[0] != kv_rank:
+            raise KernelError("latent_prepare: the norm weights do not match the ranks")
+        if rot_dims:
+            self._need(cos, "cos", torch.float32, 2)
+            self._need(sin, "sin", torch.float32, 2)
+            if tuple(cos.shape) != (N, rot_dims // 2) or tuple(sin.shape) != (N, rot_dims // 2):
+                raise KernelError("latent_prepare: cos and sin must be [tokens, rot_dims / 2]")
+        if write:
+            self._need(slot_mapping, "slot_mapping", torch.int32, 1)
+            self._need(kc_pool, "kc_pool", z.dtype, 4)
+            if tuple(kc_pool.shape[1:]) != (1, page_size, kv_rank + rot_dim):
+                raise KernelError(f"latent_prepare: the pool is {list(kc_pool.shape)}, expected [pages, 1, {page_size}, {kv_rank + rot_dim}]")
+        cq = torch.empty((N, q_rank), dtype=z.dtype, device=z.device)
+        self._check(self.lib.llmie_latent_prepare(_ptr(z), z.shape[1], q_rank, kv_rank, rot_dim, rot_dims, _ptr(q_norm), _ptr(kv_norm),
+                                                  ctypes.c_float(eps), _ptr(cos), _ptr(sin), _ptr(slot_mapping), _ptr(kc_pool), page_size,
+                                                  int(bool(write)), _ptr(cq), N, self._dt(z, "z"), self._stream()), "latent_prepare")
+        return cq
+
+    def latent_absorb(self, q, w_uk, cos, sin, num_heads, head_dim, rot_dim, rot_dims, kv_rank):
+        """``q [N, heads * (head_dim + rot_dim)]`` -> ``[N, heads * (kv_rank + rot_dim)]``: every head's unrotated part times its
+        ``[head_dim, kv_rank]`` block of ``w_uk`` (so that it meets the cached latents directly), its rotated part turned."""
+        self._need(q, "q", None, 2)
+        self._need(w_uk, "w_uk", q.dtype)
+        N = q.shape[0]
+        if q.shape[1] != num_heads * (head_dim + rot_dim) or w_uk.numel() != num_heads * head_dim * kv_rank:
+            raise KernelError("latent_absorb: q or w_uk does not match the head sizes")
+        out = torch.empty((N, num_heads * (kv_rank + rot_dim)), dtype=q.dtype, device=q.device)
+        self._check(self.lib.llmie_head_matmul(_ptr(q), q.shape[1], head_dim + rot_dim, _ptr(w_uk), _ptr(out), out.shape[1], kv_rank + rot_dim,
+                                               N, num_heads, head_dim, kv_rank, 1, rot_dim, rot_dims, _ptr(cos), _ptr(sin), _ptr(None), 0,
+                                               self._dt(q, "q"), self._stream()), "latent_absorb")
+        return out
+
+    def latent_expand(self, o_lat, w_uv, gate, gate_col, num_heads, kv_rank, v_head_dim):
+        """``o_lat [N, heads * kv_rank]`` -> ``[N, heads * v_head_dim]``: every head's row times its ``[kv_rank, v_head_dim]`` block of
+        ``w_uv``, times ``sigmoid`` of the gate columns (from ``gate_col`` of ``gate``, one per output element)."""
+        self._need(o_lat, "o_lat", None, 2)
+        self._need(w_uv, "w_uv", o_lat.dtype)
+        self._need(gate, "gate", o_lat.dtype, 2)
+        N = o_lat.shape[0]
+        if o_lat.shape[1] != num_heads * kv_rank or w_uv.numel() != num_heads * kv_rank * v_head_dim:
+            raise KernelError("latent_expand: o_lat or w_uv does not match the head sizes")
+        if gate.shape[0] != N or gate_col + num_heads * v_head_dim > gate.shape[1]:
+            raise KernelError("latent_expand: the gate columns lie outside the rows")
+        out = torch.empty((N, num_heads * v_head_dim), dtype=o_lat.dtype, device=o_lat.device)
+        self._check(self.lib.llmie_head_matmul(_ptr(o_lat), o_lat.shape[1], kv_rank, _ptr(w_uv), _ptr(out), out.shape[1], v_head_dim, N,
+                                               num_heads, kv_rank, v_head_dim, 2, 0, 0, _ptr(None), _ptr(None),
+                                               ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1],
+                                               self._dt(o_lat, "o_lat"), self._stream()), "latent_expand")
         return out
 
     def argmax(self, logits):

@@ -58,6 +58,11 @@ class LatentAttention(Mixer):
             out["sink"] = ParamSpec((Source(f"{p}.sink", (H,), INIT_SMALL),), VECTOR)
         return out
 
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        # per head [kv_rank, v_head_dim]: the layout in which ``latent_expand`` reads it (as ``w_uk`` is [head_dim, kv_rank] per head)
+        self.w_uv = tensors["w_uv"].view(self.num_heads, self.v_head_dim, self.kv_rank).transpose(1, 2).contiguous()
+
     def cache_spec(self):
         return PagedKVSpec(1, self.kv_rank + self.rot_dim, self.window, 0)
 

@@ -226,7 +226,7 @@ class TorchKernels:
 
     def latent_expand(self, o_lat, w_uv, gate, gate_col, num_heads, kv_rank, v_head_dim):
         N = o_lat.shape[0]
-        o = torch.einsum("nhr,hvr->nhv", o_lat.float().view(N, num_heads, kv_rank), w_uv.float().view(num_heads, v_head_dim, kv_rank))
+        o = torch.einsum("nhr,hrv->nhv", o_lat.float().view(N, num_heads, kv_rank), w_uv.float().view(num_heads, kv_rank, v_head_dim))
         o = o.reshape(N, -1) * torch.sigmoid(gate[:, gate_col:gate_col + num_heads * v_head_dim].float())
         return o.to(o_lat.dtype)
 
