@@ -513,6 +513,249 @@ def serving_point(folder: Path, torch, n_requests: int, seed: int, budget: int, 
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# ``--workload luvutar``: the Luvutar decoder at layer sizes of real models, beside the Qwen2 decoder of equal size.
+
+LUVUTAR_SIZES = {
+    # name: (width, heads, kv_heads, head_dim, rot_dim, q_rank, kv_rank, window, ff, streams, layers, vocab)
+    "0.5b-like": (896, 14, 2, 64, 32, 384, 256, 1024, 3584, 4, 8, 32768),
+    "3b-like": (2048, 16, 4, 128, 64, 768, 512, 2048, 8192, 4, 8, 32768),
+}
+
+
+def luvutar_config(size: str) -> dict:
+    """Layers in the order attention, latent attention, attention reading the first one's keys and values, latent attention, ..."""
+    W, H, G, d, r, qr, kr, win, ff, streams, layers, vocab = LUVUTAR_SIZES[size]
+    out = []
+    for i in range(layers):
+        if i % 2:
+            m = {"heads": H, "dim": d, "rot_dim": r, "vdim": d, "q_rank": qr, "kv_rank": kr, "scale": (d + r) ** -0.5,
+                 "mask": {"size": win}, "rot": {"base": 10000.0, "dims": r}}
+            out.append({"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "bias_max": 4096, "q_temp": {"coef": 0.1, "every": 1024}}
+            if i % 4 == 2:
+                m["kv_from"] = i - 2
+            out.append({"type": "attention", "mixer": m, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Luvutar", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "streams": streams, "layers": out}
+
+
+def qwen2_like(size: str) -> dict:
+    """The Qwen2 decoder with the same width, heads, layers and vocabulary, and a gated feed-forward of as many weights."""
+    W, H, G, d, r, qr, kr, win, ff, streams, layers, vocab = LUVUTAR_SIZES[size]
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": vocab, "hidden_size": W, "head_dim": d,
+            "intermediate_size": (2 * ff // 3 + 127) // 128 * 128, "num_hidden_layers": layers, "num_attention_heads": H,
+            "num_key_value_heads": G, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "tie_word_embeddings": False,
+            "max_position_embeddings": 32768, "use_sliding_window": False, "hidden_act": "silu"}
+
+
+def model_points(folder: Path, vocab: int, batch: int, context: int, prefill_tokens: int, steps: int, warmup: int, torch) -> dict:
+    """Decode steps (``batch`` requests at ``context`` tokens, replayed from a CUDA graph, argmax included) and one prompt of
+    ``prefill_tokens`` tokens, both as device time between two events; launches of a step and the bytes it must read."""
+    from llm_infrence_engine_b200.config import EngineConfig
+    from llm_infrence_engine_b200.engine import StepEntry, build_runner
+
+    per_seq = -(-(context + 8) // BLOCK)
+    cfg = EngineConfig(dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch, max_len=context + 8,
+                       max_num_batched_tokens=max(batch, 16), cuda_graphs=True)
+    spec, cache, runner = build_runner(folder, cfg)
+    for b in runner.bindings:
+        b.k.normal_(0, 0.5)
+        if b.v is not None:
+            b.v.normal_(0, 0.5)
+    entries = []
+    for i in range(batch):
+        cache.admit(i)
+        cache.reserve(i, 0, context)
+        entries.append(StepEntry(i, [(17 * i + 3) % vocab], context - 1, (0,)))
+    runner.step(entries)
+    cap = runner.graphs.captured[batch]
+    for _ in range(warmup):
+        cap.graph.replay()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        cap.graph.replay()
+    stop.record()
+    torch.cuda.synchronize()
+    runner.K.check_device_errors()
+    dec_ms = start.elapsed_time(stop) / steps
+    held = sum(min(context, getattr(g, "window", None) or context) * g.num_kv_heads * (g.head_dim + (g.head_dim if g.v_head_dim is None else g.v_head_dim))
+               for g in spec.cache_specs()) * 2
+    out = {"decode_ms": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3, 1), "launches_per_step": cap.launches,
+           "decode_bytes": runner.weight_bytes_per_step() + batch * held}
+    del runner, spec, cache, cap
+    torch.cuda.empty_cache()
+    cfg = EngineConfig(dtype="bfloat16", block_size=BLOCK, num_blocks=prefill_tokens // BLOCK + 2, max_seqs=1, max_len=prefill_tokens,
+                       max_num_batched_tokens=prefill_tokens, cuda_graphs=False)
+    spec, cache, runner = build_runner(folder, cfg)
+    g = torch.Generator().manual_seed(5)
+    prompt = torch.randint(0, vocab, (prefill_tokens,), generator=g).tolist()
+    times = []
+    for i in range(8):
+        cache.admit("p")
+        cache.reserve("p", 0, prefill_tokens)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        runner.step([StepEntry("p", prompt, 0, (prefill_tokens - 1,))])
+        stop.record()
+        torch.cuda.synchronize()
+        cache.free("p")
+        if i >= 3:
+            times.append(start.elapsed_time(stop))
+    runner.K.check_device_errors()
+    ms = sorted(times)[len(times) // 2]
+    out.update(prefill_ms=round(ms, 3), prefill_tok_s=round(prefill_tokens / ms * 1e3, 1))
+    del runner, spec, cache
+    torch.cuda.empty_cache()
+    return out
+
+
+def _time(fn, torch, reps: int = 20, warm: int = 3) -> float:
+    """Median-free mean device time of ``fn`` in microseconds: warm-up, then ``reps`` calls between two events."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(reps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    return start.elapsed_time(stop) / reps * 1e3
+
+
+def luvutar_kernel_points(torch, pk) -> dict:
+    """Luvutar's kernels one by one at the 3b-like layer sizes, each beside the Qwen2 kernel that does the like job at the same
+    size: microseconds, and the fraction of its roofline (bytes that must move / copy peak, or flops / bf16 peak). Inputs are
+    larger than L2 where the kernel streams memory (cache pools of several hundred MB; activations of 2,048 rows are not)."""
+    from types import SimpleNamespace
+
+    from llm_infrence_engine_b200.csrc import get_kernels
+    from llm_infrence_engine_b200.parts.attention_biased import distance_rows
+
+    K = get_kernels()
+    W, H, G, d, r, qr, kr, win, ff, S, _, _ = LUVUTAR_SIZES["3b-like"]
+    bf, dev = torch.bfloat16, "cuda"
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def entry(us, bytes_=None, flops=None):
+        e = {"us": round(us, 2)}
+        if bytes_ is not None:
+            e["frac_of_copy_peak"] = round(bytes_ / (us * 1e-6) / hbm, 4)
+        if flops is not None:
+            e["frac_of_bf16_peak"] = round(flops / (us * 1e-6) / tf, 4)
+        return e
+
+    def batch_of(lens):
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        return SimpleNamespace(seq_lens=list(lens), seq_starts_dev=torch.tensor(starts, dtype=torch.int32, device=dev),
+                               max_seq_len=max(lens), _tables={})
+
+    def tables(batch, ctx, page=BLOCK):
+        per = -(-ctx // page)
+        t = torch.zeros((batch + 1, per), dtype=torch.int32, device=dev)
+        t[:batch] = (torch.randperm(batch * per, device=dev).to(torch.int32) + 1).view(batch, per)
+        return t, batch * per + 1
+
+    rel = torch.randn(32, H, device=dev)
+    rows_of = torch.tensor(distance_rows(32, 4096.0), dtype=torch.int32, device=dev)
+    sink = torch.randn(H, device=dev)
+    for what, batch, ctx, T in (("decode", 8, 4096, 1), ("decode_b64", 64, 4096, 1), ("prefill", 1, 2048, 2048)):
+        table, pages = tables(batch, ctx)
+        N = batch * T
+        seq = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(T)
+        pos = (torch.arange(T, dtype=torch.int32, device=dev) + (ctx - T)).repeat(batch)
+        b = batch_of([T] * batch)
+        # grouped attention: Qwen2's kernels against the kernel with temperature, distance bias and a gate per head
+        kp = torch.randn(pages, G, BLOCK, d, device=dev).to(bf)
+        vp = torch.randn(pages, G, BLOCK, d, device=dev).to(bf)
+        qkv = torch.randn(N, (H + 2 * G) * d + 8 * ((H + 7) // 8), device=dev).to(bf)
+        if T == 1:
+            moved, fl = batch * ctx * 2 * G * d * 2, None
+        else:
+            moved, fl = None, 4.0 * H * d * (T * (T + 1) / 2) * batch
+        out[f"attention_{what}_qwen2"] = entry(_time(lambda: (b._tables.clear(), K.paged_attention(qkv, kp, vp, table, seq, pos, H, G, d, BLOCK, d ** -0.5, 0, ctx, batch=b)), torch), moved, fl)
+        out[f"attention_{what}_luvutar"] = entry(_time(lambda: (b._tables.clear(), K.attention_ext(qkv, 0, H, G, d, d, kp, vp, table, seq, pos, BLOCK, d ** -0.5, 0, ctx, temp=(0.1, 1024), rel=rel, rel_rows=rows_of,
+                                                                                     gate=qkv, gate_col=(H + 2 * G) * d, gate_per_head=True, batch=b)), torch), moved, fl)
+        del kp, vp
+        # latent attention: one key/value head of kv_rank + rot_dim entries, a window, a sink
+        lp = torch.randn(pages, 1, BLOCK, kr + r, device=dev).to(bf)
+        ql = torch.randn(N, H * (kr + r), device=dev).to(bf)
+        seen = min(win, ctx)
+        if T == 1:
+            moved, fl = batch * seen * (kr + r) * 2, None
+        else:
+            moved, fl = None, 2.0 * H * (2 * kr + r) * sum(min(p + 1, win) for p in range(ctx - T, ctx)) * batch
+        out[f"latent_attention_{what}_luvutar"] = entry(_time(lambda: (b._tables.clear(), K.attention_ext(ql, 0, H, 1, kr + r, kr, lp, None, table, seq, pos, BLOCK, 0.07, win, ctx, sink=sink, batch=b)), torch), moved, fl)
+        del lp
+    # norms at 2,048 rows: add + norm of one stream against update + weighted sum + norm of four
+    N = 2048
+    res, delta, w = torch.randn(N, W, device=dev), torch.randn(N, W, device=dev).to(bf), torch.ones(W, device=dev)
+    xs, mix, co, ci = torch.randn(N, S, W, device=dev), torch.eye(S, device=dev), torch.ones(S, device=dev), torch.full((S,), 0.25, device=dev)
+    out["norm_qwen2"] = entry(_time(lambda: K.add_rmsnorm(res, delta, w, 1e-6, bf), torch), N * W * (4 + 4 + 2 + 2))
+
+    def hyper():
+        K.streams_update(xs, delta, mix, co)
+        return K.streams_norm(xs, ci, w, 1e-6, bf)
+
+    out["norm_luvutar"] = entry(_time(hyper, torch), N * W * (8 * S + 2 + 2))
+    # feed-forward going in: gate/up product with SiLU against up product with GELU (equal weights: ff against 2 * (2 ff / 3))
+    h = torch.randn(N, W, device=dev).to(bf)
+    inter = (2 * ff // 3 + 127) // 128 * 128
+    wgu, wup = torch.randn(2 * inter, W, device=dev).to(bf) * 0.02, torch.randn(ff, W, device=dev).to(bf) * 0.02
+    out["ff_in_qwen2"] = entry(_time(lambda: K.gate_up_act(h, wgu, bf), torch), None, 2.0 * N * W * 2 * inter)
+    out["ff_in_luvutar"] = entry(_time(lambda: K.linear_act(h, wup, "gelu_tanh", bf), torch), None, 2.0 * N * W * ff)
+    # the per-head products around latent attention (no counterpart in Qwen2)
+    q = torch.randn(N, H * (d + r), device=dev).to(bf)
+    w_uk, w_uv = torch.randn(H * d, kr, device=dev).to(bf) * 0.05, torch.randn(H, kr, d, device=dev).to(bf) * 0.05
+    half = r // 2
+    cos, sin = torch.ones(N, half, device=dev), torch.zeros(N, half, device=dev)
+    o_lat, gate = torch.randn(N, H * kr, device=dev).to(bf), torch.randn(N, H * d, device=dev).to(bf)
+    out["latent_absorb_luvutar"] = entry(_time(lambda: K.latent_absorb(q, w_uk, cos, sin, H, d, r, r, kr), torch), None, 2.0 * N * H * d * kr)
+    out["latent_expand_luvutar"] = entry(_time(lambda: K.latent_expand(o_lat, w_uv, gate, 0, H, kr, d), torch), None, 2.0 * N * H * d * kr)
+    K.check_device_errors()
+    return out
+
+
+def luvutar_workload(a) -> int:
+    import torch
+
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    steps = min(a.steps, 256)
+    for size in LUVUTAR_SIZES:
+        vocab = LUVUTAR_SIZES[size][-1]
+        row = {}
+        for name, config in (("luvutar", luvutar_config(size)), ("qwen2", qwen2_like(size))):
+            with tempfile.TemporaryDirectory() as tmp:
+                folder = write_random_model(config, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
+                pt = model_points(folder, vocab, a.batch, a.context or 4096, a.prefill_tokens, steps, max(a.warmup, 3), torch)
+            pt["decode_frac_of_copy_peak"] = round(pt["decode_bytes"] / (pt["decode_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            row[name] = pt
+        sizes[size] = row
+    line = {"metric": f"Luvutar beside Qwen2 of equal size: decode (batch {a.batch}, context {a.context or 4096}) and prefill ({a.prefill_tokens} tokens), bf16, random weights",
+            "unit": "ms and tokens/s per size", "n_gpus": 1, "impl": "ours", "dtype": "bf16", "steps": steps, "warmup": max(a.warmup, 3),
+            "data": "synthetic: random weights (seed 0), uniform random token ids, synthetic cache contents",
+            "config": {"sizes": {k: dict(zip(("width", "heads", "kv_heads", "head_dim", "rot_dim", "q_rank", "kv_rank", "window", "ff", "streams", "layers", "vocab"), v))
+                                 for k, v in LUVUTAR_SIZES.items()}, "block_size": BLOCK, "peaks": pk["source"],
+                       "l2": "weights + cache per step larger than L2, no flush"},
+            "clocks": sampler.stop(), "sizes": sizes}
+    if a.kernels:
+        line["kernels"] = luvutar_kernel_points(torch, pk)
+    print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     global CONTEXT, PREFILL_TOKENS
     ap = argparse.ArgumentParser()
@@ -527,8 +770,10 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="measure one part only (for profiling); the JSON line then lacks the rest")
-    ap.add_argument("--workload", default="steps", choices=["steps", "serving"],
-                    help="serving: continuous batching of --requests requests (prompts U[128,2048], outputs U[64,512]) through Engine")
+    ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar"],
+                    help="serving: continuous batching of --requests requests (prompts U[128,2048], outputs U[64,512]) through Engine; "
+                         "luvutar: the Luvutar decoder at two layer sizes beside the Qwen2 decoder of equal size (decode and prefill)")
+    ap.add_argument("--kernels", action="store_true", help="luvutar: also time its kernels one by one beside their Qwen2 counterparts")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--token-budget", type=int, default=2048, help="serving: tokens per step (max_num_batched_tokens)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
@@ -538,6 +783,8 @@ def main() -> int:
     if a.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not supported")
         return 2
+    if a.workload == "luvutar":
+        return luvutar_workload(a)
     PREFILL_TOKENS = a.prefill_tokens
     shape_name, changes, shape_context = SHAPES[a.shape]
     MODEL.update(changes)
