@@ -1,0 +1,386 @@
+// Paged attention with extras (see attention_ext.cuh) on the tensor cores, bfloat16, for prompt portions and decoded tokens
+// alike: keys and values of different sizes up to a latent cache row that is key and value at once (dk = 576, dv = 512),
+// query temperature, bias by distance, sink, gate, window.
+//
+// A block works on a tile of 32 rows: row = (token of the tile, query head of the group), tokens being neighbours of one
+// request, so a chunk of 64 keys is fetched once (cp.async through the block table, two stages) for all of them. Eight
+// warps = 2 row blocks of 16 rows x 4 parts. For S = Q K^T (mma.sync m16n8k16, Q and K by ldmatrix from shared memory) a
+// part takes 16 of the chunk's 64 keys; the row's maximum and sum over the chunk meet through shared memory (two barriers of
+// the row block's 128 threads); P goes to shared memory as bfloat16 and every part multiplies the whole P by ITS quarter of
+// the value dimensions (dv / 4 columns, accumulators in registers: 64 floats per thread at dv = 512), so no product is done
+// twice. Scores, softmax and accumulators are 32-bit. Key slices (grid.z) leave partial results that the merge kernel of
+// attention_ext.cuh finishes; with one slice the block finishes its rows itself.
+#include "attention_ext.cuh"
+
+namespace {
+
+using attn_ext::Extras;
+
+constexpr int ROWS = 32, KEYS = 64, THREADS = 256;
+
+struct Params {
+    const bf16* q; int q_stride;
+    const bf16* k_pool; const bf16* v_pool;
+    const int* block_table; int max_blocks;
+    const int* token_seq; const int* positions; const int* tile_info;
+    bf16* out; float* part_acc; float* part_ml;
+    int nq, nkv, dk, dv, page_size; float scale; int window, num_splits, gh, head_chunks;
+    Extras ex;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x2_t(uint32_t& r0, uint32_t& r1, const void* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, int src_bytes) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(src_bytes));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+__device__ __forceinline__ void bar_rows(int id) { asm volatile("bar.sync %0, 128;\n" ::"r"(id)); }
+
+// NT: n8 tiles of a part's value columns (dv = 32 * NT)
+template <int NT>
+__global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int dk = P.dk, dv = P.dv;
+    const int ks = dk + 8, vs = P.v_pool ? dv + 8 : ks;        // row strides in elements: + 16 bytes keeps ldmatrix off bank conflicts
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);               // [ROWS][ks]
+    bf16* Ks = Qs + ROWS * ks;                                  // [2][KEYS][ks]
+    bf16* Vs = P.v_pool ? Ks + 2 * KEYS * ks : Ks;              // [2][KEYS][vs], or the key rows themselves
+    bf16* Ps = (P.v_pool ? Vs + 2 * KEYS * vs : Ks + 2 * KEYS * ks);   // [ROWS][KEYS + 8]
+    float* red_max = reinterpret_cast<float*>(Ps + ROWS * (KEYS + 8));  // [2][4][16]
+    float* red_sum = red_max + 2 * 4 * 16;                      // [2][4][16]
+    constexpr int PS = KEYS + 8;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int rb = warp >> 2, part = warp & 3, gid = lane >> 2, tig = lane & 3;
+    const int G = P.nq / P.nkv;
+    const int kvh = blockIdx.y / P.head_chunks, hc = blockIdx.y % P.head_chunks;
+    const int gh = P.gh;                       // heads of the group in this chunk's rows
+    const int tokens_per_tile = ROWS / gh;
+    const int split = blockIdx.z;
+
+    pdl_trigger();
+    pdl_wait();
+    int n0, ntok;
+    if (P.tile_info) { n0 = P.tile_info[2 * blockIdx.x]; ntok = P.tile_info[2 * blockIdx.x + 1]; }
+    else { n0 = blockIdx.x; ntok = 1; }
+    ntok = min(ntok, tokens_per_tile);
+    const int p_first = P.positions[n0], p_last = P.positions[n0 + ntok - 1];
+    const int lo = P.window > 0 ? max(0, p_first - P.window + 1) : 0;
+    const int hi = p_last + 1;
+    int per = (hi - lo + P.num_splits - 1) / P.num_splits;
+    per = (per + KEYS - 1) / KEYS * KEYS;
+    const int start = lo + split * per;
+    const int end = min(hi, start + per);
+    const int* table = P.block_table + (size_t)P.token_seq[n0] * P.max_blocks;
+
+    // my two rows (gid and gid + 8 of the row block): token, head, position
+    int row_pos[2], row_head[2], row_tok[2];
+    float row_factor[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = rb * 16 + gid + 8 * i;
+        const int t = r / gh, g = hc * gh + r % gh;
+        const bool ok = t < ntok && g < G && r < tokens_per_tile * gh;
+        row_tok[i] = ok ? n0 + t : -1;
+        row_head[i] = ok ? kvh * G + g : 0;
+        row_pos[i] = ok ? P.positions[n0 + t] : -1;
+        float f = P.scale;
+        if (P.ex.temp_every > 0 && ok) f = P.scale * (1.0f + P.ex.temp_coef * logf((float)((row_pos[i] + 1) / P.ex.temp_every + 1)));
+        row_factor[i] = f;
+    }
+
+    // the queries of the tile's rows
+    const int segs = dk >> 3;
+    for (int i = tid; i < ROWS * segs; i += THREADS) {
+        const int r = i / segs, sgm = i % segs;
+        const int t = r / gh, g = hc * gh + r % gh;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (t < ntok && g < G && r < tokens_per_tile * gh)
+            v = *reinterpret_cast<const uint4*>(P.q + (size_t)(n0 + t) * P.q_stride + (size_t)(kvh * G + g) * dk + sgm * 8);
+        *reinterpret_cast<uint4*>(Qs + r * ks + sgm * 8) = v;
+    }
+
+    // A chunk's rows come by cp.async, four threads to a key: one look at the block table per thread and chunk, then the
+    // thread's share of the row's 16-byte pieces (pieces quarter, quarter + 4, ...). Keys outside the slice are filled with zeros.
+    const int vsegs = dv >> 3;
+    const int my_key = tid >> 2, quarter = tid & 3;
+    auto load_chunk = [&](int base, int stage) {
+        const int key = base + my_key;
+        const bool ok = key < end && key >= lo;
+        size_t row = 0;
+        if (ok) row = ((size_t)table[key / P.page_size] * P.nkv + kvh) * P.page_size + key % P.page_size;
+        const int bytes = ok ? 16 : 0;
+        bf16* kd = Ks + (stage * KEYS + my_key) * ks;
+        const bf16* ksrc = P.k_pool + row * dk;
+        for (int sgm = quarter; sgm < segs; sgm += 4) cp_async16(kd + sgm * 8, ksrc + sgm * 8, bytes);
+        if (P.v_pool) {
+            bf16* vd = Vs + (stage * KEYS + my_key) * vs;
+            const bf16* vsrc = P.v_pool + row * dv;
+            for (int sgm = quarter; sgm < vsegs; sgm += 4) cp_async16(vd + sgm * 8, vsrc + sgm * 8, bytes);
+        }
+    };
+
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+
+    const int nchunks = end > start ? (end - start + KEYS - 1) / KEYS : 0;
+    if (nchunks > 0) load_chunk(start, 0);
+    cp_commit();
+
+    for (int c = 0; c < nchunks; ++c) {
+        const int stage = c & 1;
+        const int base = start + c * KEYS;
+        __syncthreads();                      // everyone is done with the stage that is filled next, with P and with the sums
+        if (c + 1 < nchunks) load_chunk(base + KEYS, stage ^ 1);
+        cp_commit();
+        cp_wait<1>();
+        __syncthreads();                      // chunk c (and, the first time, the queries) are in shared memory
+
+        // ---- S: my 16 keys of the chunk against the row block's 16 rows
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        {
+            // two sets of sums (even and odd steps over the inner dimension), so that four products are in flight, not two
+            float s2[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+            const bf16* qa = Qs + (rb * 16 + (lane & 15)) * ks + (lane >> 4) * 8;
+            const bf16* kb = Ks + stage * KEYS * ks + (part * 16 + (lane & 7) + ((lane >> 4) << 3)) * ks + ((lane >> 3) & 1) * 8;
+            int k0 = 0;
+            for (; k0 + 32 <= dk; k0 += 32) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3, c0, c1, c2, c3, d0, d1, d2, d3;
+                ldsm_x4(a0, a1, a2, a3, qa + k0);
+                ldsm_x4(b0, b1, b2, b3, kb + k0);
+                ldsm_x4(c0, c1, c2, c3, qa + k0 + 16);
+                ldsm_x4(d0, d1, d2, d3, kb + k0 + 16);
+                mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
+                mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+                mma_bf16(s2[0], c0, c1, c2, c3, d0, d1);
+                mma_bf16(s2[1], c0, c1, c2, c3, d2, d3);
+            }
+            if (k0 < dk) {
+                uint32_t a0, a1, a2, a3, b0, b1, b2, b3;
+                ldsm_x4(a0, a1, a2, a3, qa + k0);
+                ldsm_x4(b0, b1, b2, b3, kb + k0);
+                mma_bf16(s[0], a0, a1, a2, a3, b0, b1);
+                mma_bf16(s[1], a0, a1, a2, a3, b2, b3);
+            }
+#pragma unroll
+            for (int t = 0; t < 2; ++t)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[t][e] += s2[t][e];
+        }
+        // scale, bias, mask; element (tile t, e): row gid + 8 * (e >> 1), key base + part * 16 + t * 8 + 2 * tig + (e & 1)
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int t = 0; t < 2; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = e >> 1;
+                const int key = base + part * 16 + t * 8 + 2 * tig + (e & 1);
+                const int p = row_pos[i];
+                const bool seen = key <= p && key < end && key >= lo && (P.window <= 0 || p - key < P.window);
+                float v = -INFINITY;
+                if (seen) {
+                    v = s[t][e] * row_factor[i];
+                    if (P.ex.rel) {
+                        const int dist = p - key;
+                        const int r = dist < P.ex.n_rows_of ? P.ex.rows_of[dist] : P.ex.rel_rows - 1;
+                        v += P.ex.rel[(size_t)r * P.nq + row_head[i]];
+                    }
+                }
+                s[t][e] = v;
+                mx[i] = fmaxf(mx[i], v);
+            }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+            mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            if (tig == 0) red_max[(rb * 4 + part) * 16 + gid + 8 * i] = mx[i];
+        }
+        bar_rows(1 + rb);
+        float corr[2], m_use[2], sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float m_new = m_run[i];
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) m_new = fmaxf(m_new, red_max[(rb * 4 + q4) * 16 + gid + 8 * i]);
+            m_use[i] = m_new == -INFINITY ? 0.f : m_new;
+            corr[i] = expf(m_run[i] - m_use[i]);     // -inf before the first seen key: 0
+            m_run[i] = m_new;
+        }
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float p0 = expf(s[t][2 * i] - m_use[i]), p1 = expf(s[t][2 * i + 1] - m_use[i]);
+                const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                // the sum is taken over the rounded weights: what the product with the values uses
+                sum[i] += __low2float(pb) + __high2float(pb);
+                *reinterpret_cast<__nv_bfloat162*>(Ps + (rb * 16 + gid + 8 * i) * PS + part * 16 + t * 8 + 2 * tig) = pb;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 1);
+            sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], 2);
+            if (tig == 0) red_sum[(rb * 4 + part) * 16 + gid + 8 * i] = sum[i];
+        }
+#pragma unroll
+        for (int t = 0; t < NT; ++t) { acc[t][0] *= corr[0]; acc[t][1] *= corr[0]; acc[t][2] *= corr[1]; acc[t][3] *= corr[1]; }
+        bar_rows(1 + rb);
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float add = 0.f;
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) add += red_sum[(rb * 4 + q4) * 16 + gid + 8 * i];
+            l_run[i] = l_run[i] * corr[i] + add;
+        }
+        // ---- O += P V over my quarter of the value columns
+        {
+            const bf16* pa = Ps + (rb * 16 + (lane & 15)) * PS + (lane >> 4) * 8;
+            const bf16* vb = Vs + stage * KEYS * vs + part * (NT * 8);
+#pragma unroll
+            for (int k0 = 0; k0 < KEYS; k0 += 16) {
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4(a0, a1, a2, a3, pa + k0);
+#pragma unroll
+                for (int t = 0; t + 1 < NT; t += 2) {
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4_t(b0, b1, b2, b3, vb + (k0 + (lane & 15)) * vs + t * 8 + (lane >> 4) * 8);
+                    mma_bf16(acc[t], a0, a1, a2, a3, b0, b1);
+                    mma_bf16(acc[t + 1], a0, a1, a2, a3, b2, b3);
+                }
+                if constexpr (NT & 1) {
+                    uint32_t b0, b1;
+                    ldsm_x2_t(b0, b1, vb + (k0 + (lane & 15)) * vs + (NT - 1) * 8);
+                    mma_bf16(acc[NT - 1], a0, a1, a2, a3, b0, b1);
+                }
+            }
+        }
+    }
+    cp_wait<0>();
+
+    // ---- finish my two rows' quarter of the value columns
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (row_tok[i] < 0) continue;
+        const int n = row_tok[i], head = row_head[i];
+        if (P.num_splits == 1) {
+            float M = m_run[i], L = l_run[i], f = 1.f;
+            if (P.ex.sink) {
+                const float sk = P.ex.sink[head];
+                const float M2 = fmaxf(M, sk);
+                f = expf(M - M2);
+                L = L * f + expf(sk - M2);
+            }
+            const float inv = f / L;
+            const bf16* gate_row = P.ex.gate_mode ? reinterpret_cast<const bf16*>(P.ex.gate) + (size_t)n * P.ex.gate_stride : nullptr;
+            float gh1 = 1.f;
+            if (P.ex.gate_mode == 1) gh1 = attn_ext::sigmoidf_(to_f32(gate_row[head]));
+            bf16* o = P.out + ((size_t)n * P.nq + head) * dv + part * (NT * 8);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const int col = t * 8 + 2 * tig;
+                float y0 = acc[t][2 * i] * inv * gh1, y1 = acc[t][2 * i + 1] * inv * gh1;
+                if (P.ex.gate_mode == 2) {
+                    const bf16* gp = gate_row + (size_t)head * dv + part * (NT * 8) + col;
+                    y0 *= attn_ext::sigmoidf_(to_f32(gp[0]));
+                    y1 *= attn_ext::sigmoidf_(to_f32(gp[1]));
+                }
+                *reinterpret_cast<__nv_bfloat162*>(o + col) = __floats2bfloat162_rn(y0, y1);
+            }
+        } else {
+            const size_t slot = ((size_t)n * P.nq + head) * P.num_splits + split;
+            float* pa = P.part_acc + slot * dv + part * (NT * 8);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) *reinterpret_cast<float2*>(pa + t * 8 + 2 * tig) = make_float2(acc[t][2 * i], acc[t][2 * i + 1]);
+            if (part == 0 && tig == 0) { P.part_ml[slot * 2] = m_run[i]; P.part_ml[slot * 2 + 1] = l_run[i]; }
+        }
+    }
+}
+
+size_t smem_bytes(int dk, int dv, bool own_values) {
+    const size_t ks = dk + 8, vs = dv + 8;
+    return 2 * (ROWS * ks + 2 * KEYS * ks + (own_values ? 2 * KEYS * vs : 0) + ROWS * (KEYS + 8)) + sizeof(float) * 2 * 2 * 4 * 16;
+}
+
+template <int NT>
+int launch(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
+    static bool set = false;
+    if (!set) {
+        cudaFuncSetAttribute(attn_ext_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        set = true;
+    }
+    return launch_kernel(attn_ext_mma_kernel<NT>, grid, dim3(THREADS), smem, s, P);
+}
+
+}  // namespace
+
+// 1 if the kernel takes these sizes (bfloat16 only): dk a multiple of 16, dv one of 32 * {1, 2, 3, 4, 6, 8, 12, 16}, pages whose
+// rows start on 16-byte boundaries, and shared memory for two stages of keys.
+LLMIE_API int llmie_attention_ext_mma_fits(int dk, int dv, int own_values) {
+    const int nt = dv / 32;
+    const bool nt_ok = dv % 32 == 0 && (nt == 1 || nt == 2 || nt == 3 || nt == 4 || nt == 6 || nt == 8 || nt == 12 || nt == 16);
+    return dk % 16 == 0 && dk >= 16 && nt_ok && (own_values || dv <= dk) && smem_bytes(dk, dv, own_values != 0) <= 227 * 1024;
+}
+
+// tile_info: [tiles][2] = (first token, tokens) with at most 32 / gh tokens of one request per tile, or null: one token per tile.
+// gh = min(group, 32) heads per tile row group; scratch (num_splits > 1): N * nq * num_splits * (dv + 2) floats.
+LLMIE_API int llmie_paged_attention_ext_mma(const bf16* q, int q_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
+                                            int max_blocks, const int* token_seq, const int* positions, const int* tile_info, int tiles,
+                                            bf16* out, float* scratch, int N, int nq, int nkv, int dk, int dv, int page_size, float scale,
+                                            int window, int num_splits, float temp_coef, int temp_every, const float* rel, const int* rows_of,
+                                            int n_rows_of, int rel_rows, const float* sink, const bf16* gate, int gate_stride, int gate_mode,
+                                            cudaStream_t s) {
+    if (N <= 0 || tiles <= 0) return 0;
+    if (nkv <= 0 || nq % nkv || !llmie_attention_ext_mma_fits(dk, dv, v_pool != nullptr) || page_size <= 0 || num_splits < 1 ||
+        (num_splits > 1 && !scratch) || q_stride % 8 || ((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) || ((uintptr_t)v_pool % 16) ||
+        (rel && (!rows_of || rel_rows < 1)) || (gate_mode && !gate))
+        return LLMIE_ERR_BAD_ARGUMENT;
+    Params P;
+    P.q = q; P.q_stride = q_stride; P.k_pool = k_pool; P.v_pool = v_pool; P.block_table = block_table; P.max_blocks = max_blocks;
+    P.token_seq = token_seq; P.positions = positions; P.tile_info = tile_info; P.out = out;
+    P.part_acc = scratch; P.part_ml = scratch ? scratch + (size_t)N * nq * num_splits * dv : nullptr;
+    P.nq = nq; P.nkv = nkv; P.dk = dk; P.dv = dv; P.page_size = page_size; P.scale = scale; P.window = window; P.num_splits = num_splits;
+    const int G = nq / nkv;
+    P.gh = G < ROWS ? G : ROWS;
+    P.head_chunks = (G + P.gh - 1) / P.gh;
+    P.ex.temp_coef = temp_coef; P.ex.temp_every = temp_every; P.ex.rel = rel; P.ex.rows_of = rows_of; P.ex.n_rows_of = n_rows_of;
+    P.ex.rel_rows = rel_rows; P.ex.sink = sink; P.ex.gate = gate; P.ex.gate_stride = gate_stride; P.ex.gate_mode = gate_mode;
+    if ((long long)nkv * P.head_chunks > 65535 || num_splits > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    const dim3 grid(tiles, nkv * P.head_chunks, num_splits);
+    const size_t smem = smem_bytes(dk, dv, v_pool != nullptr);
+    int rc;
+    switch (dv / 32) {
+        case 1: rc = launch<1>(P, grid, smem, s); break;
+        case 2: rc = launch<2>(P, grid, smem, s); break;
+        case 3: rc = launch<3>(P, grid, smem, s); break;
+        case 4: rc = launch<4>(P, grid, smem, s); break;
+        case 6: rc = launch<6>(P, grid, smem, s); break;
+        case 8: rc = launch<8>(P, grid, smem, s); break;
+        case 12: rc = launch<12>(P, grid, smem, s); break;
+        default: rc = launch<16>(P, grid, smem, s); break;
+    }
+    if (rc) return rc;
+    if (num_splits > 1) {
+        attn_ext::attn_ext_combine_kernel<bf16><<<N * nq, 64, 0, s>>>(P.part_acc, P.part_ml, out, nq, dv, num_splits, P.ex);
+        rc = launch_status();
+    }
+    return rc;
+}

@@ -63,6 +63,8 @@ class CudaKernels:
         self.use_tc_qkv = True         # prompt portions, head size 64: q/k/v product with bias, rotation and cache write in one kernel ...
         self.tc_qkv_min_rows = 2048    # ... from this many rows on: below, the library product + the rotation kernel are 4 to 10 % of a step faster
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
+        self.use_mma_attention_ext = True    # bfloat16 attention with extras on the tensor cores (else the generic kernel)
+        self.head_matmul_library_rows = 64   # per-head products of latent attention: from this many rows on, one batched library product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
         # A library product that is to be added into the residual stream is kept here until the next kernel that reads
@@ -86,7 +88,8 @@ class CudaKernels:
         for fn in ("llmie_embed", "llmie_feed_tokens", "llmie_zero_fresh_state", "llmie_rope_tables", "llmie_add_rmsnorm", "llmie_rope_kv_write", "llmie_silu_mul",
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample",
                    "llmie_streams_expand", "llmie_streams_update", "llmie_streams_norm", "llmie_latent_prepare", "llmie_head_matmul",
-                   "llmie_kv_store", "llmie_act", "llmie_paged_attention_ext_f32", "llmie_paged_attention_ext_bf16"):
+                   "llmie_kv_store", "llmie_act", "llmie_paged_attention_ext_f32", "llmie_paged_attention_ext_bf16", "llmie_paged_attention_ext_mma",
+                   "llmie_attention_ext_mma_fits"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = None
@@ -861,10 +864,34 @@ class CudaKernels:
             if gate.shape[0] != N or gate_col + (num_heads if gate_per_head else num_heads * v_head_dim) > gate.shape[1]:
                 raise KernelError("attention_ext: the gate columns lie outside the rows")
         out = torch.empty((N, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
+        esize = q.element_size()
+        if (dt == 1 and self.use_mma_attention_ext and batch is not None and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0
+                and self.lib.llmie_attention_ext_mma_fits(head_dim, v_head_dim, int(v_pool is not None))):
+            # bfloat16: the tensor-core kernel, for prompt portions and decoded tokens alike. A tile is up to 32 rows of
+            # (token, head of the group); the keys are cut into slices when the tiles alone would leave multiprocessors idle.
+            group = num_heads // num_kv_heads
+            heads_per_tile = min(group, 32)
+            if batch.max_seq_len == 1:
+                tiles, tile_info = N, None
+            else:
+                tiles, tile_info = self._tiles(batch, 32 // heads_per_tile, q.device)
+            blocks = tiles * num_kv_heads * -(-group // heads_per_tile)
+            span = min(max_context, window) if window else max_context
+            splits = num_splits or max(1, min((2 * self.num_sms) // max(blocks, 1), -(-span // 64) // 2, 32))
+            scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
+            self._check(self.lib.llmie_paged_attention_ext_mma(
+                ctypes.c_void_p(q.data_ptr() + q_col * esize), q.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+                _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads, head_dim,
+                v_head_dim, page_size, ctypes.c_float(scale), int(window), splits, ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel),
+                _ptr(rel_rows), 0 if rel_rows is None else rel_rows.shape[0], 0 if rel is None else rel.shape[0], _ptr(sink),
+                ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1], gate_mode,
+                self._stream()), "attention_ext (tensor cores)")
+            if splits > 1:
+                self.launches += 1
+            return out
         slice_keys = 0 if num_splits else self.slice_keys
         splits = num_splits or self.attention_slices(max_context)
         scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
-        esize = q.element_size()
         fn = self.lib.llmie_paged_attention_ext_f32 if dt == 0 else self.lib.llmie_paged_attention_ext_bf16
         self._check(fn(ctypes.c_void_p(q.data_ptr() + q_col * esize), q.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table),
                        block_table.shape[1], _ptr(token_seq), _ptr(positions), _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads,
@@ -914,8 +941,16 @@ class CudaKernels:
         if q.shape[1] != num_heads * (head_dim + rot_dim) or w_uk.numel() != num_heads * head_dim * kv_rank:
             raise KernelError("latent_absorb: q or w_uk does not match the head sizes")
         out = torch.empty((N, num_heads * (kv_rank + rot_dim)), dtype=q.dtype, device=q.device)
+        mode = 1
+        if q.dtype == torch.bfloat16 and self.use_cublas and N >= self.head_matmul_library_rows:
+            # many rows: the products of all heads as one batched library product (written straight into its columns of the
+            # result); the kernel then only turns and copies the rotated parts
+            torch.bmm(q.view(N, num_heads, head_dim + rot_dim)[:, :, :head_dim].transpose(0, 1), w_uk.view(num_heads, head_dim, kv_rank),
+                      out=out.view(N, num_heads, kv_rank + rot_dim)[:, :, :kv_rank].transpose(0, 1))
+            self.launches += 1
+            mode = 3
         self._check(self.lib.llmie_head_matmul(_ptr(q), q.shape[1], head_dim + rot_dim, _ptr(w_uk), _ptr(out), out.shape[1], kv_rank + rot_dim,
-                                               N, num_heads, head_dim, kv_rank, 1, rot_dim, rot_dims, _ptr(cos), _ptr(sin), _ptr(None), 0,
+                                               N, num_heads, head_dim, kv_rank, mode, rot_dim, rot_dims, _ptr(cos), _ptr(sin), _ptr(None), 0,
                                                self._dt(q, "q"), self._stream()), "latent_absorb")
         return out
 
@@ -931,8 +966,14 @@ class CudaKernels:
         if gate.shape[0] != N or gate_col + num_heads * v_head_dim > gate.shape[1]:
             raise KernelError("latent_expand: the gate columns lie outside the rows")
         out = torch.empty((N, num_heads * v_head_dim), dtype=o_lat.dtype, device=o_lat.device)
+        mode = 2
+        if o_lat.dtype == torch.bfloat16 and self.use_cublas and N >= self.head_matmul_library_rows:
+            torch.bmm(o_lat.view(N, num_heads, kv_rank).transpose(0, 1), w_uv.view(num_heads, kv_rank, v_head_dim),
+                      out=out.view(N, num_heads, v_head_dim).transpose(0, 1))
+            self.launches += 1
+            mode = 4   # the kernel only multiplies by the gate
         self._check(self.lib.llmie_head_matmul(_ptr(o_lat), o_lat.shape[1], kv_rank, _ptr(w_uv), _ptr(out), out.shape[1], v_head_dim, N,
-                                               num_heads, kv_rank, v_head_dim, 2, 0, 0, _ptr(None), _ptr(None),
+                                               num_heads, kv_rank, v_head_dim, mode, 0, 0, _ptr(None), _ptr(None),
                                                ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.shape[1],
                                                self._dt(o_lat, "o_lat"), self._stream()), "latent_expand")
         return out

@@ -49,7 +49,9 @@ __global__ void latent_prepare_kernel(const T* __restrict__ z, int z_stride, int
 }
 
 constexpr int TOK = 8;
-enum { MODE_PLAIN = 0, MODE_ABSORB = 1, MODE_EXPAND = 2 };
+// ABSORB_TAIL and GATE_ONLY: the products were made elsewhere (a batched library product wrote them into `out`); only the
+// copy of the rotated parts, or the multiplication by the gate, is left.
+enum { MODE_PLAIN = 0, MODE_ABSORB = 1, MODE_EXPAND = 2, MODE_ABSORB_TAIL = 3, MODE_GATE_ONLY = 4 };
 
 template <typename T>
 __global__ void __launch_bounds__(128) head_matmul_kernel(const T* __restrict__ x, int x_stride, int x_head, const T* __restrict__ M,
@@ -61,13 +63,23 @@ __global__ void __launch_bounds__(128) head_matmul_kernel(const T* __restrict__ 
     pdl_wait();
     const int n0 = blockIdx.x * TOK, h = blockIdx.y;
     const int nt = min(TOK, N - n0);
+    if (mode == MODE_GATE_ONLY) {
+        for (int i = threadIdx.x; i < nt * J; i += blockDim.x) {
+            const int t = i / J, j = i % J;
+            T* o = out + (size_t)(n0 + t) * out_stride + (size_t)h * out_head + j;
+            *o = from_f32<T>(to_f32(*o) * (1.0f / (1.0f + expf(-to_f32(gate[(size_t)(n0 + t) * gate_stride + (size_t)h * J + j])))));
+        }
+        return;
+    }
+    const bool tail_only = mode == MODE_ABSORB_TAIL;
+    if (tail_only) mode = MODE_ABSORB;
     for (int i = threadIdx.x; i < TOK * K; i += blockDim.x) {
         const int t = i / K, k = i % K;
         xs[i] = t < nt ? to_f32(x[(size_t)(n0 + t) * x_stride + (size_t)h * x_head + k]) : 0.f;
     }
     __syncthreads();
     const T* Mh = M + (size_t)h * K * J;
-    for (int j = threadIdx.x; j < J; j += blockDim.x) {
+    for (int j = threadIdx.x; j < (tail_only ? 0 : J); j += blockDim.x) {
         float acc[TOK];
 #pragma unroll
         for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
@@ -139,8 +151,8 @@ LLMIE_API int llmie_head_matmul(const void* x, int x_stride, int x_head, const v
                                 int K, int J, int mode, int R, int rot_dims, const float* cos_t, const float* sin_t, const void* gate,
                                 int gate_stride, int dtype, cudaStream_t s) {
     if (N <= 0) return 0;
-    if (K < 1 || J < 1 || H < 1 || mode < 0 || mode > 2 || (mode == 1 && (rot_dims > R || (rot_dims & 1) || (rot_dims && (!cos_t || !sin_t)))) ||
-        (mode == 2 && !gate))
+    if (K < 1 || J < 1 || H < 1 || mode < 0 || mode > 4 || ((mode == 1 || mode == 3) && (rot_dims > R || (rot_dims & 1) || (rot_dims && (!cos_t || !sin_t)))) ||
+        ((mode == 2 || mode == 4) && !gate))
         return LLMIE_ERR_BAD_ARGUMENT;
     if (dtype == DT_F32)
         return head_matmul<float>((const float*)x, x_stride, x_head, (const float*)M, (float*)out, out_stride, out_head, N, H, K, J, mode, R, rot_dims, cos_t, sin_t, (const float*)gate, gate_stride, s);

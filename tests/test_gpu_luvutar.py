@@ -3,6 +3,7 @@ implementation: whole prompts, decoding token by token, portions down to two tok
 decoding, greedy generation through the entry point, decode steps from CUDA graphs, and inputs made so that a far key,
 a window's edge or a sink shows in the result."""
 import math
+from types import SimpleNamespace
 
 import pytest
 import torch
@@ -107,7 +108,8 @@ def paged(N_ctx, page, nkv, dk, dv, dtype, seed=0, shared_values=False):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,dk,dv,shared", [(4, 2, 16, 8, False), (6, 1, 64, 64, False), (5, 1, 20, 12, True), (8, 1, 128, 96, True),
-                                                 (3, 3, 24, 40, False), (2, 1, 288, 256, True), (16, 2, 32, 32, False)])
+                                                 (3, 3, 24, 40, False), (2, 1, 288, 256, True), (16, 2, 32, 32, False), (14, 2, 64, 64, False),
+                                                 (16, 1, 576, 512, True), (40, 1, 48, 32, True), (4, 4, 128, 128, False), (6, 2, 80, 192, False)])
 def test_attention_ext_every_extra(K, dtype, nq, nkv, dk, dv, shared):
     """Positions spread over a request of 1,300 tokens (two key slices), each extra alone and all together."""
     ctx_len, page = 1300, 16
@@ -128,13 +130,17 @@ def test_attention_ext_every_extra(K, dtype, nq, nkv, dk, dv, shared):
         "all": {"window": 700, "temp": (0.4, 16), "rel": rel, "rel_rows": rows, "sink": sink, "gate": gate, "gate_col": 1, "gate_per_head": True},
     }
     dev = lambda t: t.cuda() if isinstance(t, torch.Tensor) else t
+    # with a description of the step (here: one request that brings all ten tokens) bfloat16 sizes that fit take the tensor-core kernel
+    step = SimpleNamespace(seq_lens=[N], seq_starts_dev=torch.tensor([0, N], dtype=torch.int32).cuda(), max_seq_len=N, _tables={})
     for what, kw in variants.items():
         window = kw.pop("window", 0)
         want = TorchKernels().attention_ext(q, 8, nq, nkv, dk, dv, k_pool, v_pool, table, seq, pos, page, 0.3, window, ctx_len, **kw)
-        got = K.attention_ext(q.cuda(), 8, nq, nkv, dk, dv, k_pool.cuda(), dev(v_pool), table.cuda(), seq.cuda(), pos.cuda(), page, 0.3, window,
-                              ctx_len, **{k: dev(v) for k, v in kw.items()})
-        # (scores of ten and more: their exponentials carry a few 1e-7 of relative error each)
-        close(got, want, dtype, f"attention_ext {what}", scale=5.0 if dtype == "float32" else 1.0)
+        for batch in (None, step):
+            got = K.attention_ext(q.cuda(), 8, nq, nkv, dk, dv, k_pool.cuda(), dev(v_pool), table.cuda(), seq.cuda(), pos.cuda(), page, 0.3, window,
+                                  ctx_len, batch=batch, **{k: dev(v) for k, v in kw.items()})
+            # (scores of ten and more, sums over up to 576 products: their exponentials carry a few 1e-7 of relative error each)
+            close(got, want, dtype, f"attention_ext {what} ({'generic' if batch is None else 'with the step'})",
+                  scale=5.0 * max(1.0, dk / 64) ** 0.5 if dtype == "float32" else None)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -153,7 +159,9 @@ def test_attention_ext_one_key_stands_out(K, dtype):
         q = (unit * 4.0).to(TD[dtype])[None]
         args = (1, 1, dk, dv, kp.cuda(), v_pool.cuda(), table.cuda(), torch.ones(1, dtype=torch.int32).cuda(),
                 torch.tensor([p], dtype=torch.int32).cuda(), page, 1.0, window, ctx_len)
+        one = SimpleNamespace(seq_lens=[1], seq_starts_dev=torch.tensor([0, 1], dtype=torch.int32).cuda(), max_seq_len=1, _tables={})
         got = K.attention_ext(q.cuda(), 0, *args).float().cpu()[0]
+        assert (K.attention_ext(q.cuda(), 0, *args, batch=one).float().cpu()[0] - got).abs().max() < 2e-2   # the tensor-core kernel in bfloat16
         if seen:
             assert (got - v[j, 0].float()).abs().max() < 2e-2, f"key {j} from position {p} (window {window}) should own the result"
         else:
