@@ -36,19 +36,27 @@ struct Extras {
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
-// Finish one (token, head): fold in the sink, divide, gate.
+// What the sums of one (token, head) are multiplied by at the end: the sink joins the denominator, then the division and the
+// gate per head. The same arithmetic wherever a (token, head) is finished, so that a result does not depend on whether its
+// keys were cut into slices.
 template <typename T>
-__device__ __forceinline__ float finish(float A, float M, float L, const Extras& ex, int head, int dim, int dv, const T* gate_row) {
+__device__ __forceinline__ float finish_scale(float M, float L, const Extras& ex, int head, const T* gate_row) {
+    float f = 1.f;
     if (ex.sink) {
         const float sk = ex.sink[head];
         const float M2 = fmaxf(M, sk);
-        const float f = expf(M - M2);   // M = -inf (no visible key) gives 0
-        A *= f;
+        f = expf(M - M2);   // M = -inf (no visible key) gives 0
         L = L * f + expf(sk - M2);
     }
-    float o = A / L;
-    if (ex.gate_mode == 1) o *= sigmoidf_(to_f32(gate_row[head]));
-    else if (ex.gate_mode == 2) o *= sigmoidf_(to_f32(gate_row[(size_t)head * dv + dim]));
+    float g = f / L;
+    if (ex.gate_mode == 1) g *= sigmoidf_(to_f32(gate_row[head]));
+    return g;
+}
+
+template <typename T>
+__device__ __forceinline__ float finish(float A, float M, float L, const Extras& ex, int head, int dim, int dv, const T* gate_row) {
+    float o = A * finish_scale<T>(M, L, ex, head, gate_row);
+    if (ex.gate_mode == 2) o *= sigmoidf_(to_f32(gate_row[(size_t)head * dv + dim]));
     return o;
 }
 
@@ -221,23 +229,47 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_ext_kernel(
     }
 }
 
-// The slices of one (token, head) merged in the order of the slices, then finished (sink, division, gate).
+// The slices of one (token, head) merged, then finished (sink, division, gate). A slice's weight e^(m_s - M) is computed once
+// (the first warp, a slice per lane) and kept in shared memory; every sum runs in one fixed order.
 template <typename T>
 __global__ void attn_ext_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, T* __restrict__ out,
                                         int nq, int dv, int num_splits, Extras ex) {
+    constexpr int KEPT = 128;
+    __shared__ float w_s[KEPT];
+    __shared__ float scale_s, max_s;
     const size_t th = blockIdx.x;  // token * nq + head
     const int n = (int)(th / nq), head = (int)(th % nq);
     const float* ml = part_ml + th * num_splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < num_splits; ++s) M = fmaxf(M, ml[2 * s]);
-    float L = 0.f;
-    for (int s = 0; s < num_splits; ++s) L = fmaf(ml[2 * s + 1], ml[2 * s] > -INFINITY ? expf(ml[2 * s] - M) : 0.f, L);
-    const T* gate_row = ex.gate_mode ? reinterpret_cast<const T*>(ex.gate) + (size_t)n * ex.gate_stride : nullptr;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float M = -INFINITY;
+        for (int s = lane; s < num_splits; s += 32) M = fmaxf(M, ml[2 * s]);
+        M = warp_max(M);
+        float L = 0.f;
+        for (int s = lane; s < num_splits; s += 32) {
+            const float w = ml[2 * s] > -INFINITY ? expf(ml[2 * s] - M) : 0.f;
+            if (s < KEPT) w_s[s] = w;
+            L = fmaf(ml[2 * s + 1], w, L);
+        }
+        L = warp_sum(L);
+        if (lane == 0) {
+            scale_s = finish_scale<T>(M, L, ex, head, ex.gate_mode ? reinterpret_cast<const T*>(ex.gate) + (size_t)n * ex.gate_stride : nullptr);
+            max_s = M;
+        }
+    }
+    __syncthreads();
+    const float g = scale_s, M = max_s;
+    const T* gate_row = ex.gate_mode == 2 ? reinterpret_cast<const T*>(ex.gate) + (size_t)n * ex.gate_stride + (size_t)head * dv : nullptr;
+    const float* acc = part_acc + th * num_splits * dv;
     for (int dim = threadIdx.x; dim < dv; dim += blockDim.x) {
         float A = 0.f;
-        for (int s = 0; s < num_splits; ++s)
-            A = fmaf(part_acc[(th * num_splits + s) * dv + dim], ml[2 * s] > -INFINITY ? expf(ml[2 * s] - M) : 0.f, A);
-        out[th * dv + dim] = from_f32<T>(finish<T>(A, M, L, ex, head, dim, dv, gate_row));
+        for (int s = 0; s < num_splits; ++s) {
+            const float w = s < KEPT ? w_s[s] : (ml[2 * s] > -INFINITY ? expf(ml[2 * s] - M) : 0.f);
+            A = fmaf(acc[(size_t)s * dv + dim], w, A);
+        }
+        float o = A * g;
+        if (gate_row) o *= sigmoidf_(to_f32(gate_row[dim]));
+        out[th * dv + dim] = from_f32<T>(o);
     }
 }
 
@@ -310,7 +342,7 @@ int paged_attention_ext(const T* q, int q_stride, const T* k_pool, const T* v_po
 #undef LLMIE_EXT
     if (rc) return rc;
     if (num_splits > 1) {
-        attn_ext_combine_kernel<T><<<N * nq, 64, 0, s>>>(part_acc, part_ml, out, nq, dv, num_splits, ex);
+        attn_ext_combine_kernel<T><<<N * nq, 128, 0, s>>>(part_acc, part_ml, out, nq, dv, num_splits, ex);
         rc = launch_status();
     }
     return rc;

@@ -64,6 +64,10 @@ class CudaKernels:
         self.tc_qkv_min_rows = 2048    # ... from this many rows on: below, the library product + the rotation kernel are 4 to 10 % of a step faster
         self.tc_max_rows = 128        # batches up to this many rows take the small-batch tensor-core product
         self.use_mma_attention_ext = True    # bfloat16 attention with extras on the tensor cores (else the generic kernel)
+        # ... on tiles of at most this many rows. The kernel also has tiles of 64 and 128 rows (a chunk's keys fetched once for
+        # more rows); measured slower at 2,048 tokens (heads of 128: 311 -> 415 us): their registers leave one block per
+        # multiprocessor where tiles of 32 rows leave two, and the kernel waits on its barriers, not on the keys
+        self.attention_ext_tile_rows = 32
         self.head_matmul_library_rows = 64   # per-head products of latent attention: from this many rows on, one batched library product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
@@ -74,6 +78,9 @@ class CudaKernels:
         # normalises in one pass: (streams, the sublayer's result, mix, out coefficients)
         self._pending_streams: Optional[tuple] = None
         self._fresh_zero: Optional[torch.Tensor] = None   # the zeroed tensor that ``zeros_like_rows`` handed out last
+        # ``zeros_like_rows`` hands out views of one float32 buffer that is zero between uses: the stream kernels that read a
+        # sublayer's result out of it set it back to zero on their way (no fill kernel per sublayer)
+        self._zero_rows: Optional[torch.Tensor] = None
         self._error_flag: Optional[torch.Tensor] = None
         self._acc_qkv: Optional[torch.Tensor] = None   # float32 sums of a decode step's q/k/v product, read by the attention kernel
         self._dirty_qkv: Optional[torch.Tensor] = None  # those sums while they still wait to be cleared
@@ -119,7 +126,7 @@ class CudaKernels:
         self._pending_streams = None
         self._fresh_zero = None
         self._dirty_qkv = None
-        for t in [self._acc, self._acc_qkv, *self._retired_acc]:
+        for t in [self._acc, self._acc_qkv, self._zero_rows, *self._retired_acc]:
             if t is not None:
                 try:
                     t.zero_()
@@ -229,8 +236,8 @@ class CudaKernels:
             xs, y, mix, coef_out = self._pending_streams
             self._pending_streams = None
             N, S, H = xs.shape
-            self._check(self.lib.llmie_streams_update(_ptr(xs), _ptr(y), self._dt(y, "y"), _ptr(mix), _ptr(coef_out), N, S, H, self._stream()),
-                        "streams_update")
+            self._check(self.lib.llmie_streams_update(_ptr(xs), _ptr(y), self._dt(y, "y"), int(self._clears(y)), _ptr(mix), _ptr(coef_out), N, S, H,
+                                                      self._stream()), "streams_update")
 
     def _take_pending(self, residual, out_dtype):
         """The put-off addend for ``residual`` if there is one that the norm kernel can add on its way (same dtype as its output)."""
@@ -730,9 +737,17 @@ class CudaKernels:
     # ------------------------------------------------------------------ several residual streams
     def zeros_like_rows(self, streams):
         """A zeroed float32 ``[N, hidden]`` for a sublayer to add its result into (``streams`` is ``[N, S, hidden]``)."""
-        self._fresh_zero = torch.zeros((streams.shape[0], streams.shape[-1]), dtype=torch.float32, device=streams.device)
-        self.launches += 1
+        N, H = streams.shape[0], streams.shape[-1]
+        if self._zero_rows is None or self._zero_rows.numel() < N * H or self._zero_rows.device != streams.device:
+            if self._zero_rows is not None:
+                self._retired_acc.append(self._zero_rows)   # a captured graph may still add into it and clear it
+            self._zero_rows = torch.zeros(max(N * H, 1 << 20), dtype=torch.float32, device=streams.device)
+        self._fresh_zero = self._zero_rows[: N * H].view(N, H)
         return self._fresh_zero
+
+    def _clears(self, y) -> bool:
+        return (self._zero_rows is not None and y.dtype == torch.float32
+                and y.untyped_storage().data_ptr() == self._zero_rows.untyped_storage().data_ptr())
 
     def streams_expand(self, x, streams: int):
         self.flush()
@@ -788,9 +803,13 @@ class CudaKernels:
             self._need(rows, "rows", torch.int32, 1)
         n_out = N if rows is None else rows.shape[0]
         out = torch.empty((n_out, H), dtype=out_dtype, device=xs.device)
-        self._check(self.lib.llmie_streams_norm(_ptr(xs), _ptr(y), 0 if y is None else self._dt(y, "y"), _ptr(mix), _ptr(coef_out), _ptr(coef_in),
-                                                _ptr(weight), _ptr(out), _DT[out_dtype], _ptr(rows), n_out, S, H, ctypes.c_float(eps),
-                                                self._stream()), "streams_norm")
+        clears = y is not None and self._clears(y)
+        self._check(self.lib.llmie_streams_norm(_ptr(xs), _ptr(y), 0 if y is None else self._dt(y, "y"), int(clears), _ptr(mix), _ptr(coef_out),
+                                                _ptr(coef_in), _ptr(weight), _ptr(out), _DT[out_dtype], _ptr(rows), n_out, S, H,
+                                                ctypes.c_float(eps), self._stream()), "streams_norm")
+        if clears and rows is not None:
+            y.zero_()   # only the chosen rows were read and cleared; the buffer must be zero for its next user
+            self.launches += 1
         return out
 
     # ------------------------------------------------------------------ a product with an activation behind it
@@ -865,24 +884,30 @@ class CudaKernels:
                 raise KernelError("attention_ext: the gate columns lie outside the rows")
         out = torch.empty((N, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
         esize = q.element_size()
-        if (dt == 1 and self.use_mma_attention_ext and batch is not None and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0
-                and self.lib.llmie_attention_ext_mma_fits(head_dim, v_head_dim, int(v_pool is not None))):
-            # bfloat16: the tensor-core kernel, for prompt portions and decoded tokens alike. A tile is up to 32 rows of
-            # (token, head of the group); the keys are cut into slices when the tiles alone would leave multiprocessors idle.
+        max_rows = 0
+        if dt == 1 and self.use_mma_attention_ext and batch is not None and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0:
+            max_rows = self.lib.llmie_attention_ext_mma_fits(head_dim, v_head_dim, int(v_pool is not None))
+        if max_rows:
+            # bfloat16: the tensor-core kernel, for prompt portions and decoded tokens alike. A tile is 32, 64 or 128 rows of
+            # (token, head of the group), as many as the step's longest request can fill; the keys are cut into slices when
+            # the tiles alone would leave multiprocessors idle.
             group = num_heads // num_kv_heads
             heads_per_tile = min(group, 32)
+            tile_rows = 32
+            while tile_rows < min(max_rows, self.attention_ext_tile_rows) and tile_rows < batch.max_seq_len * heads_per_tile:
+                tile_rows *= 2
             if batch.max_seq_len == 1:
                 tiles, tile_info = N, None
             else:
-                tiles, tile_info = self._tiles(batch, 32 // heads_per_tile, q.device)
+                tiles, tile_info = self._tiles(batch, tile_rows // heads_per_tile, q.device)
             blocks = tiles * num_kv_heads * -(-group // heads_per_tile)
             span = min(max_context, window) if window else max_context
             splits = num_splits or max(1, min((2 * self.num_sms) // max(blocks, 1), -(-span // 64) // 2, 32))
             scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
             self._check(self.lib.llmie_paged_attention_ext_mma(
                 ctypes.c_void_p(q.data_ptr() + q_col * esize), q.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
-                _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads, head_dim,
-                v_head_dim, page_size, ctypes.c_float(scale), int(window), splits, ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel),
+                _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, tile_rows, _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads,
+                head_dim, v_head_dim, page_size, ctypes.c_float(scale), int(window), splits, ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel),
                 _ptr(rel_rows), 0 if rel_rows is None else rel_rows.shape[0], 0 if rel is None else rel.shape[0], _ptr(sink),
                 ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1], gate_mode,
                 self._stream()), "attention_ext (tensor cores)")

@@ -53,50 +53,74 @@ constexpr int TOK = 8;
 // copy of the rotated parts, or the multiplication by the gate, is left.
 enum { MODE_PLAIN = 0, MODE_ABSORB = 1, MODE_EXPAND = 2, MODE_ABSORB_TAIL = 3, MODE_GATE_ONLY = 4 };
 
+// A block: up to TOK tokens, one head, 32 result columns (lane = column). Its four warps take a quarter of the inner dimension
+// each, in order, and their partial sums are added in the order of the warps: every result is one fixed sequence of 32-bit
+// multiply-adds, whatever the batch holds.
 template <typename T>
 __global__ void __launch_bounds__(128) head_matmul_kernel(const T* __restrict__ x, int x_stride, int x_head, const T* __restrict__ M,
                                                          T* __restrict__ out, int out_stride, int out_head, int N, int K, int J, int mode,
                                                          int R, int rot_dims, const float* __restrict__ cos_t,
                                                          const float* __restrict__ sin_t, const T* __restrict__ gate, int gate_stride) {
-    extern __shared__ __align__(16) float xs[];   // [TOK][K]
+    extern __shared__ __align__(16) float xs[];   // [TOK][K], then [4][TOK][32] partial sums
+    float* part = xs + TOK * K;
     pdl_trigger();
     pdl_wait();
-    const int n0 = blockIdx.x * TOK, h = blockIdx.y;
+    const int n0 = blockIdx.x * TOK, h = blockIdx.y, j0 = blockIdx.z * 32;
     const int nt = min(TOK, N - n0);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (mode == MODE_GATE_ONLY) {
-        for (int i = threadIdx.x; i < nt * J; i += blockDim.x) {
-            const int t = i / J, j = i % J;
+        for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+            const int t = i / 32, j = j0 + i % 32;
+            if (j >= J) continue;
             T* o = out + (size_t)(n0 + t) * out_stride + (size_t)h * out_head + j;
             *o = from_f32<T>(to_f32(*o) * (1.0f / (1.0f + expf(-to_f32(gate[(size_t)(n0 + t) * gate_stride + (size_t)h * J + j])))));
         }
         return;
     }
-    const bool tail_only = mode == MODE_ABSORB_TAIL;
-    if (tail_only) mode = MODE_ABSORB;
-    for (int i = threadIdx.x; i < TOK * K; i += blockDim.x) {
-        const int t = i / K, k = i % K;
-        xs[i] = t < nt ? to_f32(x[(size_t)(n0 + t) * x_stride + (size_t)h * x_head + k]) : 0.f;
-    }
-    __syncthreads();
-    const T* Mh = M + (size_t)h * K * J;
-    for (int j = threadIdx.x; j < (tail_only ? 0 : J); j += blockDim.x) {
+    if (mode != MODE_ABSORB_TAIL) {
+        for (int i = threadIdx.x; i < TOK * K; i += blockDim.x) {
+            const int t = i / K, k = i % K;
+            xs[i] = t < nt ? to_f32(x[(size_t)(n0 + t) * x_stride + (size_t)h * x_head + k]) : 0.f;
+        }
+        __syncthreads();
+        const int j = j0 + lane;
+        const int kq = (K + 3) / 4;
+        const int k_lo = warp * kq, k_hi = min(K, k_lo + kq);
         float acc[TOK];
 #pragma unroll
         for (int t = 0; t < TOK; ++t) acc[t] = 0.f;
-        for (int k = 0; k < K; ++k) {
-            const float w = to_f32(Mh[(size_t)k * J + j]);
+        if (j < J) {
+            const T* col = M + (size_t)h * K * J + j;
+            int k = k_lo;
+            for (; k + 8 <= k_hi; k += 8) {   // eight loads in flight
+                float w[8];
 #pragma unroll
-            for (int t = 0; t < TOK; ++t) acc[t] = fmaf(xs[t * K + k], w, acc[t]);
+                for (int u = 0; u < 8; ++u) w[u] = to_f32(col[(size_t)(k + u) * J]);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+#pragma unroll
+                    for (int t = 0; t < TOK; ++t) acc[t] = fmaf(xs[t * K + k + u], w[u], acc[t]);
+            }
+            for (; k < k_hi; ++k) {
+                const float w = to_f32(col[(size_t)k * J]);
+#pragma unroll
+                for (int t = 0; t < TOK; ++t) acc[t] = fmaf(xs[t * K + k], w, acc[t]);
+            }
         }
 #pragma unroll
-        for (int t = 0; t < TOK; ++t) {
-            if (t >= nt) continue;
-            float v = acc[t];
-            if (mode == MODE_EXPAND) v *= 1.0f / (1.0f + expf(-to_f32(gate[(size_t)(n0 + t) * gate_stride + (size_t)h * J + j])));
-            out[(size_t)(n0 + t) * out_stride + (size_t)h * out_head + j] = from_f32<T>(v);
+        for (int t = 0; t < TOK; ++t) part[(warp * TOK + t) * 32 + lane] = acc[t];
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * 32; i += blockDim.x) {
+            const int t = i / 32, jj = j0 + i % 32;
+            if (jj >= J) continue;
+            float v = part[(0 * TOK + t) * 32 + i % 32];
+#pragma unroll
+            for (int w = 1; w < 4; ++w) v += part[(w * TOK + t) * 32 + i % 32];
+            if (mode == MODE_EXPAND) v *= 1.0f / (1.0f + expf(-to_f32(gate[(size_t)(n0 + t) * gate_stride + (size_t)h * J + jj])));
+            out[(size_t)(n0 + t) * out_stride + (size_t)h * out_head + jj] = from_f32<T>(v);
         }
     }
-    if (mode != MODE_ABSORB) return;
+    if ((mode != MODE_ABSORB && mode != MODE_ABSORB_TAIL) || blockIdx.z != 0) return;
     const int half = rot_dims >> 1;
     for (int i = threadIdx.x; i < nt * R; i += blockDim.x) {
         const int t = i / R, e = i % R, n = n0 + t;
@@ -124,10 +148,11 @@ int prepare(const T* z, int z_stride, int q_rank, int kv_rank, int rot_dim, int 
 template <typename T>
 int head_matmul(const T* x, int x_stride, int x_head, const T* M, T* out, int out_stride, int out_head, int N, int H, int K, int J, int mode,
                 int R, int rot_dims, const float* cos_t, const float* sin_t, const T* gate, int gate_stride, cudaStream_t s) {
-    const size_t smem = sizeof(float) * TOK * (size_t)K;
-    if (smem > 200 * 1024 || H > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    const size_t smem = sizeof(float) * (TOK * (size_t)K + 4 * TOK * 32);
+    const int jchunks = mode == MODE_ABSORB_TAIL ? 1 : (J + 31) / 32;   // the tail alone is one block's work per tokens and head
+    if (smem > 200 * 1024 || H > 65535 || jchunks > 65535) return LLMIE_ERR_BAD_ARGUMENT;
     if (smem > 48 * 1024) cudaFuncSetAttribute(head_matmul_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_kernel(head_matmul_kernel<T>, dim3((N + TOK - 1) / TOK, H), dim3(128), smem, s, x, x_stride, x_head, M, out, out_stride,
+    return launch_kernel(head_matmul_kernel<T>, dim3((N + TOK - 1) / TOK, H, jchunks), dim3(128), smem, s, x, x_stride, x_head, M, out, out_stride,
                          out_head, N, K, J, mode, R, rot_dims, cos_t, sin_t, gate, gate_stride);
 }
 

@@ -31,7 +31,7 @@ __device__ __forceinline__ void mix_one(float* x, float y, const float* mix_s, c
 }
 
 template <int MAXS, typename TY, typename TO>
-__global__ void streams_norm_kernel(float* __restrict__ xs, const TY* __restrict__ y, const float* __restrict__ mix,
+__global__ void streams_norm_kernel(float* __restrict__ xs, TY* __restrict__ y, int clear_y, const float* __restrict__ mix,
                                     const float* __restrict__ coef_out, const float* __restrict__ coef_in,
                                     const float* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ rows, int S, int H,
                                     float eps) {
@@ -56,6 +56,7 @@ __global__ void streams_norm_kernel(float* __restrict__ xs, const TY* __restrict
             if (s < S) x[s] = base[(size_t)s * H + c];
         if (y) {
             mix_one<MAXS, TY>(x, to_f32(y[(size_t)r * H + c]), mix_s, out_s, S);
+            if (clear_y) y[(size_t)r * H + c] = from_f32<TY>(0.f);
             if (!rows) {
 #pragma unroll
                 for (int s = 0; s < MAXS; ++s)
@@ -76,7 +77,7 @@ __global__ void streams_norm_kernel(float* __restrict__ xs, const TY* __restrict
 }
 
 template <int MAXS, typename TY>
-__global__ void streams_update_kernel(float* __restrict__ xs, const TY* __restrict__ y, const float* __restrict__ mix,
+__global__ void streams_update_kernel(float* __restrict__ xs, TY* __restrict__ y, int clear_y, const float* __restrict__ mix,
                                       const float* __restrict__ coef_out, int S, int H, long long total) {
     __shared__ float mix_s[MAXS * MAXS], out_s[MAXS];
     pdl_trigger();
@@ -94,6 +95,7 @@ __global__ void streams_update_kernel(float* __restrict__ xs, const TY* __restri
     for (int s = 0; s < MAXS; ++s)
         if (s < S) x[s] = base[(size_t)s * H];
     mix_one<MAXS, TY>(x, to_f32(y[i]), mix_s, out_s, S);
+    if (clear_y) y[i] = from_f32<TY>(0.f);
 #pragma unroll
     for (int s = 0; s < MAXS; ++s)
         if (s < S) base[(size_t)s * H] = x[s];
@@ -111,32 +113,32 @@ __global__ void streams_expand_kernel(const float* __restrict__ x, float* __rest
 }
 
 template <int MAXS, typename TY, typename TO>
-int launch_norm(float* xs, const TY* y, const float* mix, const float* coef_out, const float* coef_in, const float* weight, TO* out,
+int launch_norm(float* xs, TY* y, int clear_y, const float* mix, const float* coef_out, const float* coef_in, const float* weight, TO* out,
                 const int* rows, int n_out, int S, int H, float eps, cudaStream_t s) {
     const size_t smem = sizeof(float) * ((size_t)H + 36 + S * S + 2 * S);
     if (smem > 200 * 1024) return LLMIE_ERR_BAD_ARGUMENT;
     if (smem > 48 * 1024) cudaFuncSetAttribute(streams_norm_kernel<MAXS, TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     int threads = 64;
     while (threads < 512 && threads * 2 <= H) threads *= 2;
-    return launch_kernel(streams_norm_kernel<MAXS, TY, TO>, dim3(n_out), dim3(threads), smem, s, xs, y, mix, coef_out, coef_in, weight, out,
+    return launch_kernel(streams_norm_kernel<MAXS, TY, TO>, dim3(n_out), dim3(threads), smem, s, xs, y, clear_y, mix, coef_out, coef_in, weight, out,
                          rows, S, H, eps);
 }
 
 template <typename TY, typename TO>
-int norm_by_streams(float* xs, const TY* y, const float* mix, const float* coef_out, const float* coef_in, const float* weight, TO* out,
+int norm_by_streams(float* xs, TY* y, int clear_y, const float* mix, const float* coef_out, const float* coef_in, const float* weight, TO* out,
                     const int* rows, int n_out, int S, int H, float eps, cudaStream_t s) {
-    if (S <= 4) return launch_norm<4, TY, TO>(xs, y, mix, coef_out, coef_in, weight, out, rows, n_out, S, H, eps, s);
-    if (S <= 8) return launch_norm<8, TY, TO>(xs, y, mix, coef_out, coef_in, weight, out, rows, n_out, S, H, eps, s);
-    return launch_norm<16, TY, TO>(xs, y, mix, coef_out, coef_in, weight, out, rows, n_out, S, H, eps, s);
+    if (S <= 4) return launch_norm<4, TY, TO>(xs, y, clear_y, mix, coef_out, coef_in, weight, out, rows, n_out, S, H, eps, s);
+    if (S <= 8) return launch_norm<8, TY, TO>(xs, y, clear_y, mix, coef_out, coef_in, weight, out, rows, n_out, S, H, eps, s);
+    return launch_norm<16, TY, TO>(xs, y, clear_y, mix, coef_out, coef_in, weight, out, rows, n_out, S, H, eps, s);
 }
 
 template <typename TY>
-int update_by_streams(float* xs, const TY* y, const float* mix, const float* coef_out, int N, int S, int H, cudaStream_t s) {
+int update_by_streams(float* xs, TY* y, int clear_y, const float* mix, const float* coef_out, int N, int S, int H, cudaStream_t s) {
     const long long total = (long long)N * H;
     const dim3 grid((unsigned)((total + 255) / 256));
-    if (S <= 4) return launch_kernel(streams_update_kernel<4, TY>, grid, dim3(256), 0, s, xs, y, mix, coef_out, S, H, total);
-    if (S <= 8) return launch_kernel(streams_update_kernel<8, TY>, grid, dim3(256), 0, s, xs, y, mix, coef_out, S, H, total);
-    return launch_kernel(streams_update_kernel<16, TY>, grid, dim3(256), 0, s, xs, y, mix, coef_out, S, H, total);
+    if (S <= 4) return launch_kernel(streams_update_kernel<4, TY>, grid, dim3(256), 0, s, xs, y, clear_y, mix, coef_out, S, H, total);
+    if (S <= 8) return launch_kernel(streams_update_kernel<8, TY>, grid, dim3(256), 0, s, xs, y, clear_y, mix, coef_out, S, H, total);
+    return launch_kernel(streams_update_kernel<16, TY>, grid, dim3(256), 0, s, xs, y, clear_y, mix, coef_out, S, H, total);
 }
 
 }  // namespace
@@ -148,25 +150,26 @@ LLMIE_API int llmie_streams_expand(const float* x, float* xs, int N, int S, int 
     return launch_kernel(streams_expand_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, x, xs, S, H, total);
 }
 
-// y_dtype: DT_F32 or DT_BF16.
-LLMIE_API int llmie_streams_update(float* xs, const void* y, int y_dtype, const float* mix, const float* coef_out, int N, int S, int H,
+// y_dtype: DT_F32 or DT_BF16. clear_y: y is set to zero after it was read (a buffer that the next sublayer adds into again).
+LLMIE_API int llmie_streams_update(float* xs, void* y, int y_dtype, int clear_y, const float* mix, const float* coef_out, int N, int S, int H,
                                    cudaStream_t s) {
     if (N <= 0) return 0;
     if (S < 1 || S > 16 || H < 1 || !y || !mix || !coef_out) return LLMIE_ERR_BAD_ARGUMENT;
-    if (y_dtype == DT_F32) return update_by_streams<float>(xs, (const float*)y, mix, coef_out, N, S, H, s);
-    return update_by_streams<bf16>(xs, (const bf16*)y, mix, coef_out, N, S, H, s);
+    if (y_dtype == DT_F32) return update_by_streams<float>(xs, (float*)y, clear_y, mix, coef_out, N, S, H, s);
+    return update_by_streams<bf16>(xs, (bf16*)y, clear_y, mix, coef_out, N, S, H, s);
 }
 
 // y == nullptr: no update, only the norm of the weighted sum. rows != nullptr: chosen tokens, nothing stored back.
-LLMIE_API int llmie_streams_norm(float* xs, const void* y, int y_dtype, const float* mix, const float* coef_out, const float* coef_in,
+// With rows and clear_y only the chosen rows of y are cleared.
+LLMIE_API int llmie_streams_norm(float* xs, void* y, int y_dtype, int clear_y, const float* mix, const float* coef_out, const float* coef_in,
                                  const float* weight, void* out, int out_dtype, const int* rows, int n_out, int S, int H, float eps,
                                  cudaStream_t s) {
     if (n_out <= 0) return 0;
     if (S < 1 || S > 16 || H < 1 || !coef_in || !weight || (y && (!mix || !coef_out))) return LLMIE_ERR_BAD_ARGUMENT;
     if (out_dtype == DT_F32) {
-        if (y_dtype == DT_F32 || !y) return norm_by_streams<float, float>(xs, (const float*)y, mix, coef_out, coef_in, weight, (float*)out, rows, n_out, S, H, eps, s);
-        return norm_by_streams<bf16, float>(xs, (const bf16*)y, mix, coef_out, coef_in, weight, (float*)out, rows, n_out, S, H, eps, s);
+        if (y_dtype == DT_F32 || !y) return norm_by_streams<float, float>(xs, (float*)y, clear_y, mix, coef_out, coef_in, weight, (float*)out, rows, n_out, S, H, eps, s);
+        return norm_by_streams<bf16, float>(xs, (bf16*)y, clear_y, mix, coef_out, coef_in, weight, (float*)out, rows, n_out, S, H, eps, s);
     }
-    if (y_dtype == DT_F32 || !y) return norm_by_streams<float, bf16>(xs, (const float*)y, mix, coef_out, coef_in, weight, (bf16*)out, rows, n_out, S, H, eps, s);
-    return norm_by_streams<bf16, bf16>(xs, (const bf16*)y, mix, coef_out, coef_in, weight, (bf16*)out, rows, n_out, S, H, eps, s);
+    if (y_dtype == DT_F32 || !y) return norm_by_streams<float, bf16>(xs, (float*)y, clear_y, mix, coef_out, coef_in, weight, (bf16*)out, rows, n_out, S, H, eps, s);
+    return norm_by_streams<bf16, bf16>(xs, (bf16*)y, clear_y, mix, coef_out, coef_in, weight, (bf16*)out, rows, n_out, S, H, eps, s);
 }

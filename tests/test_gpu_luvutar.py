@@ -114,7 +114,7 @@ def test_attention_ext_every_extra(K, dtype, nq, nkv, dk, dv, shared):
     """Positions spread over a request of 1,300 tokens (two key slices), each extra alone and all together."""
     ctx_len, page = 1300, 16
     k_pool, v_pool, table, _, _ = paged(ctx_len, page, nkv, dk, dv, dtype, 3, shared)
-    pos = torch.tensor([0, 1, 15, 16, 17, 100, 1023, 1024, 1025, 1299], dtype=torch.int32)
+    pos = torch.tensor([0, 1, 15, 16, 17, 100, 1023, 1024, 1025, 1299] + list(range(1180, 1299, 3)), dtype=torch.int32).sort().values
     N = pos.shape[0]
     q = rnd(N, nq * dk + 8, seed=5, scale=0.5).to(TD[dtype])
     seq = torch.ones(N, dtype=torch.int32)
@@ -140,7 +140,7 @@ def test_attention_ext_every_extra(K, dtype, nq, nkv, dk, dv, shared):
                                   ctx_len, batch=batch, **{k: dev(v) for k, v in kw.items()})
             # (scores of ten and more, sums over up to 576 products: their exponentials carry a few 1e-7 of relative error each)
             close(got, want, dtype, f"attention_ext {what} ({'generic' if batch is None else 'with the step'})",
-                  scale=5.0 * max(1.0, dk / 64) ** 0.5 if dtype == "float32" else None)
+                  scale=8.0 * max(1.0, dk / 64) ** 0.5 if dtype == "float32" else None)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
