@@ -25,6 +25,7 @@ struct Params {
     const int* token_seq; const int* positions; const int* tile_info;
     bf16* out; float* part_acc; float* part_ml;
     int nq, nkv, dk, dv, page_size; float scale; int window, num_splits, gh, head_chunks;
+    int bias_in_smem;   // the distance table's rows (as 16-bit numbers) and this block's heads' columns of it are copied to shared memory
     Extras ex;
 };
 
@@ -67,6 +68,8 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     bf16* Ps = (P.v_pool ? Vs + 2 * KEYS * vs : Ks + 2 * KEYS * ks);   // [ROWS_T][KEYS + 8]
     float* red_max = reinterpret_cast<float*>(Ps + ROWS_T * (KEYS + 8));  // [2 R][4][16]
     float* red_sum = red_max + 2 * R * 4 * 16;                  // [2 R][4][16]
+    float* bias_val = red_sum + 2 * R * 4 * 16;                 // [rel_rows][gh]: the distance table's columns of this block's heads
+    unsigned short* bias_row = reinterpret_cast<unsigned short*>(bias_val + (P.bias_in_smem ? P.ex.rel_rows * P.gh : 0));   // [n_rows_of]
     constexpr int PS = KEYS + 8;
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -78,6 +81,13 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     const int split = blockIdx.z;
 
     pdl_trigger();
+    if (P.bias_in_smem) {   // weights of the model: fetched before the wait for the kernel before
+        for (int i = tid; i < P.ex.rel_rows * gh; i += THREADS) {
+            const int g = hc * gh + i % gh;
+            bias_val[i] = g < G ? P.ex.rel[(size_t)(i / gh) * P.nq + kvh * G + g] : 0.f;
+        }
+        for (int i = tid; i < P.ex.n_rows_of; i += THREADS) bias_row[i] = (unsigned short)P.ex.rows_of[i];
+    }
     pdl_wait();
     int n0, ntok;
     if (P.tile_info) { n0 = P.tile_info[2 * blockIdx.x]; ntok = P.tile_info[2 * blockIdx.x + 1]; }
@@ -93,7 +103,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     const int* table = P.block_table + (size_t)P.token_seq[n0] * P.max_blocks;
 
     // my rows (gid and gid + 8 of each of my row blocks): token, head, position
-    int row_pos[R][2], row_head[R][2], row_tok[R][2];
+    int row_pos[R][2], row_head[R][2], row_tok[R][2], row_g[R][2];
     float row_factor[R][2];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -104,6 +114,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
             const bool ok = t < ntok && g < G;
             row_tok[r][i] = ok ? n0 + t : -1;
             row_head[r][i] = ok ? kvh * G + g : 0;
+            row_g[r][i] = ok ? row % gh : 0;
             row_pos[r][i] = ok ? P.positions[n0 + t] : -1;
             float f = P.scale;
             if (P.ex.temp_every > 0 && ok) f = P.scale * (1.0f + P.ex.temp_coef * logf((float)((row_pos[r][i] + 1) / P.ex.temp_every + 1)));
@@ -233,8 +244,13 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
                         v = (s[r][t][e] + s2[r][t][e]) * row_factor[r][i];
                         if (P.ex.rel) {
                             const int dist = p - key;
-                            const int br = dist < P.ex.n_rows_of ? P.ex.rows_of[dist] : P.ex.rel_rows - 1;
-                            v += P.ex.rel[(size_t)br * P.nq + row_head[r][i]];
+                            if (P.bias_in_smem) {
+                                const int br = dist < P.ex.n_rows_of ? bias_row[dist] : P.ex.rel_rows - 1;
+                                v += bias_val[br * gh + row_g[r][i]];
+                            } else {
+                                const int br = dist < P.ex.n_rows_of ? P.ex.rows_of[dist] : P.ex.rel_rows - 1;
+                                v += P.ex.rel[(size_t)br * P.nq + row_head[r][i]];
+                            }
                         }
                     }
                     s[r][t][e] = v;
@@ -377,6 +393,9 @@ size_t smem_bytes(int dk, int dv, bool own_values, int R) {
     return 2 * (rows * ks + 2 * KEYS * ks + (own_values ? 2 * KEYS * vs : 0) + rows * (KEYS + 8)) + sizeof(float) * 2 * 2 * R * 4 * 16;
 }
 
+// what a copy of the distance table in shared memory takes (see Params::bias_in_smem)
+size_t bias_bytes(int rel_rows, int gh, int n_rows_of) { return sizeof(float) * (size_t)rel_rows * gh + 2 * (size_t)((n_rows_of + 1) & ~1); }
+
 template <int NT, int R>
 int launch(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
     static bool set = false;
@@ -431,7 +450,12 @@ LLMIE_API int llmie_paged_attention_ext_mma(const bf16* q, int q_stride, const b
     if ((long long)nkv * P.head_chunks > 65535 || num_splits > 65535) return LLMIE_ERR_BAD_ARGUMENT;
     const dim3 grid(tiles, nkv * P.head_chunks, num_splits);
     const int R = tile_rows / ROWS;
-    const size_t smem = smem_bytes(dk, dv, v_pool != nullptr, R);
+    size_t smem = smem_bytes(dk, dv, v_pool != nullptr, R);
+    P.bias_in_smem = 0;
+    if (rel && rel_rows <= 65535 && bias_bytes(rel_rows, P.gh, n_rows_of) <= 32 * 1024 && smem + bias_bytes(rel_rows, P.gh, n_rows_of) <= 227 * 1024) {
+        P.bias_in_smem = 1;
+        smem += bias_bytes(rel_rows, P.gh, n_rows_of);
+    }
     int rc = LLMIE_ERR_BAD_ARGUMENT;
 #define LLMIE_MMA(NTV)                                                         \
     if (R == 1) rc = launch<NTV, 1>(P, grid, smem, s);                         \
