@@ -263,7 +263,8 @@ __global__ void attn_ext_combine_kernel(const float* __restrict__ part_acc, cons
     const float* acc = part_acc + th * num_splits * dv;
     for (int dim = threadIdx.x; dim < dv; dim += blockDim.x) {
         float A = 0.f;
-        for (int s = 0; s < num_splits; ++s) {
+#pragma unroll 4
+        for (int s = 0; s < num_splits; ++s) {   // (unrolled: four slices' loads are in flight; the order of the additions stays)
             const float w = s < KEPT ? w_s[s] : (ml[2 * s] > -INFINITY ? expf(ml[2 * s] - M) : 0.f);
             A = fmaf(acc[(size_t)s * dv + dim], w, A);
         }
