@@ -18,7 +18,7 @@ from pathlib import Path
 
 
 def main(argv=None) -> int:
-    ap = argparse.ArgumentParser(prog="python -m llm_infrence_engine_b200", description="Generate tokens with a Qwen2 model folder on one GPU.")
+    ap = argparse.ArgumentParser(prog="python -m llm_infrence_engine_b200", description="Generate tokens with a model folder (Qwen2 or Luvutar; config.json names the architecture) on one GPU.")
     ap.add_argument("--model", required=True, help="folder with config.json and *.safetensors")
     ap.add_argument("--dtype", default="bfloat16", choices=["float32", "bfloat16"])
     ap.add_argument("--device", default="cuda:0")
