@@ -56,16 +56,16 @@ __device__ __forceinline__ void bar_rows(int id) { asm volatile("bar.sync %0, 12
 // NT: n8 tiles of a part's value columns (dv = 32 * NT). R: row blocks of 16 rows per warp: a tile has 32 * R rows, and a warp
 // (rb, part) works on the row blocks rb * R .. rb * R + R - 1, so a chunk's keys and values are fetched and read from shared
 // memory once for R times the rows (prompt portions; decoded tokens take R = 1).
-template <int NT, int R>
+template <int NT, int R, int ST>
 __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int ROWS_T = ROWS * R;
     const int dk = P.dk, dv = P.dv;
     const int ks = dk + 8, vs = P.v_pool ? dv + 8 : ks;        // row strides in elements: + 16 bytes keeps ldmatrix off bank conflicts
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);               // [ROWS_T][ks]
-    bf16* Ks = Qs + ROWS_T * ks;                                // [2][KEYS][ks]
-    bf16* Vs = P.v_pool ? Ks + 2 * KEYS * ks : Ks;              // [2][KEYS][vs], or the key rows themselves
-    bf16* Ps = (P.v_pool ? Vs + 2 * KEYS * vs : Ks + 2 * KEYS * ks);   // [ROWS_T][KEYS + 8]
+    bf16* Ks = Qs + ROWS_T * ks;                                // [ST][KEYS][ks]
+    bf16* Vs = P.v_pool ? Ks + ST * KEYS * ks : Ks;             // [ST][KEYS][vs], or the key rows themselves
+    bf16* Ps = (P.v_pool ? Vs + ST * KEYS * vs : Ks + ST * KEYS * ks);   // [ROWS_T][KEYS + 8]
     float* red_max = reinterpret_cast<float*>(Ps + ROWS_T * (KEYS + 8));  // [2 R][4][16]
     float* red_sum = red_max + 2 * R * 4 * 16;                  // [2 R][4][16]
     float* bias_val = red_sum + 2 * R * 4 * 16;                 // [rel_rows][gh]: the distance table's columns of this block's heads
@@ -170,17 +170,23 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
         l_run[r][0] = l_run[r][1] = 0.f;
     }
 
+    // A ring of ST stages: the chunks c + 1 .. c + ST - 1 are on their way while chunk c is worked on (ST = 2 for prompt
+    // portions, whose keys come from L2; more for decoded tokens, whose keys come from memory). One group of copies per chunk,
+    // also an empty one, so that the count of groups in flight says which chunk has landed.
     const int nchunks = end > start ? (end - start + KEYS - 1) / KEYS : 0;
-    if (nchunks > 0) load_chunk(start, 0);
-    cp_commit();
+#pragma unroll
+    for (int i = 0; i < ST - 1; ++i) {
+        if (i < nchunks) load_chunk(start + i * KEYS, i);
+        cp_commit();
+    }
 
     for (int c = 0; c < nchunks; ++c) {
-        const int stage = c & 1;
+        const int stage = c % ST;
         const int base = start + c * KEYS;
         __syncthreads();                      // everyone is done with the stage that is filled next, with P and with the sums
-        if (c + 1 < nchunks) load_chunk(base + KEYS, stage ^ 1);
+        if (c + ST - 1 < nchunks) load_chunk(base + (ST - 1) * KEYS, (c + ST - 1) % ST);
         cp_commit();
-        cp_wait<1>();
+        cp_wait<ST - 1>();
         __syncthreads();                      // chunk c (and, the first time, the queries) are in shared memory
         if (r_live == 0) continue;
 
@@ -388,22 +394,32 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
         }
 }
 
-size_t smem_bytes(int dk, int dv, bool own_values, int R) {
+size_t smem_bytes(int dk, int dv, bool own_values, int R, int stages = 2) {
     const size_t ks = dk + 8, vs = dv + 8, rows = (size_t)ROWS * R;
-    return 2 * (rows * ks + 2 * KEYS * ks + (own_values ? 2 * KEYS * vs : 0) + rows * (KEYS + 8)) + sizeof(float) * 2 * 2 * R * 4 * 16;
+    return 2 * (rows * ks + stages * KEYS * ks + (own_values ? stages * KEYS * vs : 0) + rows * (KEYS + 8)) + sizeof(float) * 2 * 2 * R * 4 * 16;
 }
 
 // what a copy of the distance table in shared memory takes (see Params::bias_in_smem)
 size_t bias_bytes(int rel_rows, int gh, int n_rows_of) { return sizeof(float) * (size_t)rel_rows * gh + 2 * (size_t)((n_rows_of + 1) & ~1); }
 
-template <int NT, int R>
-int launch(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
+constexpr int DEEP = 4;   // stages of the ring for decoded tokens, where shared memory has room for them
+
+template <int NT, int R, int ST>
+int launch_st(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
     static bool set = false;
     if (!set) {
-        cudaFuncSetAttribute(attn_ext_mma_kernel<NT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(attn_ext_mma_kernel<NT, R, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         set = true;
     }
-    return launch_kernel(attn_ext_mma_kernel<NT, R>, grid, dim3(THREADS), smem, s, P);
+    return launch_kernel(attn_ext_mma_kernel<NT, R, ST>, grid, dim3(THREADS), smem, s, P);
+}
+
+template <int NT, int R>
+int launch(const Params& P, dim3 grid, size_t smem, cudaStream_t s, bool deep) {
+    if constexpr (R == 1) {
+        if (deep) return launch_st<NT, 1, DEEP>(P, grid, smem, s);
+    }
+    return launch_st<NT, R, 2>(P, grid, smem, s);
 }
 
 // the most row blocks per warp that registers allow for value rows of 32 * nt entries
@@ -450,7 +466,12 @@ LLMIE_API int llmie_paged_attention_ext_mma(const bf16* q, int q_stride, const b
     if ((long long)nkv * P.head_chunks > 65535 || num_splits > 65535) return LLMIE_ERR_BAD_ARGUMENT;
     const dim3 grid(tiles, nkv * P.head_chunks, num_splits);
     const int R = tile_rows / ROWS;
-    size_t smem = smem_bytes(dk, dv, v_pool != nullptr, R);
+    // decoded tokens alone (no tiles of several tokens): a deeper ring where two blocks still fit on a multiprocessor with it
+    // (measured at heads of 128, where it costs the second block: batch 64 at 4,096 keys 162 -> 225 us; heads of 64 gain 2 %)
+    const size_t table_bytes = rel ? bias_bytes(rel_rows, G < ROWS ? G : ROWS, n_rows_of) : 0;
+    const bool deep = !tile_info && R == 1 &&
+                      2 * (smem_bytes(dk, dv, v_pool != nullptr, 1, DEEP) + (table_bytes <= 32 * 1024 ? table_bytes : 0) + 1024) <= 227 * 1024;
+    size_t smem = smem_bytes(dk, dv, v_pool != nullptr, R, deep ? DEEP : 2);
     P.bias_in_smem = 0;
     if (rel && rel_rows <= 65535 && bias_bytes(rel_rows, P.gh, n_rows_of) <= 32 * 1024 && smem + bias_bytes(rel_rows, P.gh, n_rows_of) <= 227 * 1024) {
         P.bias_in_smem = 1;
@@ -458,9 +479,9 @@ LLMIE_API int llmie_paged_attention_ext_mma(const bf16* q, int q_stride, const b
     }
     int rc = LLMIE_ERR_BAD_ARGUMENT;
 #define LLMIE_MMA(NTV)                                                         \
-    if (R == 1) rc = launch<NTV, 1>(P, grid, smem, s);                         \
-    else if (R == 2 && NTV <= 8) rc = launch<NTV, (NTV <= 8 ? 2 : 1)>(P, grid, smem, s); \
-    else if (R == 4 && NTV <= 2) rc = launch<NTV, (NTV <= 2 ? 4 : 1)>(P, grid, smem, s);
+    if (R == 1) rc = launch<NTV, 1>(P, grid, smem, s, deep);                         \
+    else if (R == 2 && NTV <= 8) rc = launch<NTV, (NTV <= 8 ? 2 : 1)>(P, grid, smem, s, false); \
+    else if (R == 4 && NTV <= 2) rc = launch<NTV, (NTV <= 2 ? 4 : 1)>(P, grid, smem, s, false);
     switch (dv / 32) {
         case 1: LLMIE_MMA(1) break;
         case 2: LLMIE_MMA(2) break;
