@@ -68,6 +68,7 @@ class CudaKernels:
         # more rows); measured slower at 2,048 tokens (heads of 128: 311 -> 415 us): their registers leave one block per
         # multiprocessor where tiles of 32 rows leave two, and the kernel waits on its barriers, not on the keys
         self.attention_ext_tile_rows = 32
+        self.use_fa_attention_ext = True     # prompt portions with heads of 64 / 128: the kernel in which a warp owns 16 rows and all keys of a chunk
         self.head_matmul_library_rows = 64   # per-head products of latent attention: from this many rows on, one batched library product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
         self._acc: Optional[torch.Tensor] = None  # float32 zeros: split-K products add into it, their consumer clears it again
@@ -96,7 +97,7 @@ class CudaKernels:
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample",
                    "llmie_streams_expand", "llmie_streams_update", "llmie_streams_norm", "llmie_latent_prepare", "llmie_head_matmul",
                    "llmie_kv_store", "llmie_act", "llmie_paged_attention_ext_f32", "llmie_paged_attention_ext_bf16", "llmie_paged_attention_ext_mma",
-                   "llmie_attention_ext_mma_fits"):
+                   "llmie_attention_ext_mma_fits", "llmie_paged_attention_ext_fa", "llmie_attention_ext_fa_fits"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = None
@@ -885,7 +886,27 @@ class CudaKernels:
         out = torch.empty((N, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
         esize = q.element_size()
         max_rows = 0
-        if dt == 1 and self.use_mma_attention_ext and batch is not None and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0:
+        tensor_cores = dt == 1 and self.use_mma_attention_ext and batch is not None and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0
+        if (tensor_cores and self.use_fa_attention_ext and batch.max_seq_len > 1
+                and self.lib.llmie_attention_ext_fa_fits(head_dim, v_head_dim, int(v_pool is not None), num_heads // num_kv_heads)):
+            # steps with prompt portions, heads of 64 or 128: tiles of 64 rows, a warp to 16 rows and all of a chunk's keys
+            group = num_heads // num_kv_heads
+            tiles, tile_info = self._tiles(batch, 64 // min(group, 64), q.device)
+            blocks = tiles * num_kv_heads * -(-group // 64)
+            span = min(max_context, window) if window else max_context
+            splits = num_splits or max(1, min((2 * self.num_sms) // max(blocks, 1), -(-span // 64) // 2, 32))
+            scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
+            self._check(self.lib.llmie_paged_attention_ext_fa(
+                ctypes.c_void_p(q.data_ptr() + q_col * esize), q.shape[1], _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
+                _ptr(token_seq), _ptr(positions), _ptr(tile_info), tiles, _ptr(out), _ptr(scratch), N, num_heads, num_kv_heads, head_dim,
+                v_head_dim, page_size, ctypes.c_float(scale), int(window), splits, ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel),
+                _ptr(rel_rows), 0 if rel_rows is None else rel_rows.shape[0], 0 if rel is None else rel.shape[0], _ptr(sink),
+                ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1], gate_mode,
+                self._stream()), "attention_ext (tensor cores, a warp to a row block)")
+            if splits > 1:
+                self.launches += 1
+            return out
+        if tensor_cores:
             max_rows = self.lib.llmie_attention_ext_mma_fits(head_dim, v_head_dim, int(v_pool is not None))
         if max_rows:
             # bfloat16: the tensor-core kernel, for prompt portions and decoded tokens alike. A tile is 32, 64 or 128 rows of

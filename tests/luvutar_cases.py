@@ -1,6 +1,6 @@
 """Small Luvutar models and the ways of running them that the CPU and the GPU tests share.
 
-The configurations differ from each other in every size and option: streams (none, 1, 2, 5), groups of 1, 2 and 5
+The configurations differ from each other in every size and option: streams (none, 1, 2, 3, 5), groups of 1, 2, 3, 4 and 5
 query heads per key/value head, values longer and shorter than keys, a rotation over part of the rotated entries,
 windows shorter and longer than a page, distance tables of 6, 8 and 16 rows, a layer without feed-forward, layers
 that read another layer's keys and values. The engine runs them through ``TraceReplayer`` (the step function, the
@@ -66,6 +66,13 @@ CASES = {
         _ff(_biased(6, 1, 32, 40, 0.18, 12, temp=(0.7, 2)), 96),
         _ff(_latent(4, 16, 16, 32, 48, 64, 0.12, window=16, rot=(50.0, 16)), 72),
     ]), {"l0.mix.rel": 8}, 16),
+    # heads of 64 and of 128 (keys) / 64 (values): in bfloat16 their prompt portions take the tensor-core kernel of their own
+    "T": (_model(75, 56, 1e-6, 3, [
+        _ff(_biased(6, 2, 64, 64, 0.12, 40, temp=(0.3, 11)), 48),
+        _ff(_latent(2, 16, 16, 32, 24, 48, 0.2, window=30, rot=(1000.0, 16)), None),
+        _ff(_biased(4, 1, 128, 64, 0.09, 25, temp=(0.2, 6)), 40),
+        _ff(_biased(6, 2, 64, 64, 0.12, 40, kv_from=0), 32),
+    ]), {"l0.mix.rel": 10, "l2.mix.rel": 8, "l3.mix.rel": 10}, 16),
     "S": (_model(50, 32, 1e-5, 1, [
         _ff(_latent(1, 8, 8, 8, 16, 16, 0.3, window=5, rot=(20.0, 8)), 32),
         _ff(_biased(2, 1, 8, 16, 0.4, 9, temp=(1.0, 4)), 16),

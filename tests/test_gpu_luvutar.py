@@ -109,7 +109,8 @@ def paged(N_ctx, page, nkv, dk, dv, dtype, seed=0, shared_values=False):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nq,nkv,dk,dv,shared", [(4, 2, 16, 8, False), (6, 1, 64, 64, False), (5, 1, 20, 12, True), (8, 1, 128, 96, True),
                                                  (3, 3, 24, 40, False), (2, 1, 288, 256, True), (16, 2, 32, 32, False), (14, 2, 64, 64, False),
-                                                 (16, 1, 576, 512, True), (40, 1, 48, 32, True), (4, 4, 128, 128, False), (6, 2, 80, 192, False)])
+                                                 (16, 1, 576, 512, True), (40, 1, 48, 32, True), (4, 4, 128, 128, False), (6, 2, 80, 192, False),
+                                                 (7, 1, 64, 128, False), (16, 4, 128, 64, False), (70, 1, 64, 64, False)])
 def test_attention_ext_every_extra(K, dtype, nq, nkv, dk, dv, shared):
     """Positions spread over a request of 1,300 tokens (two key slices), each extra alone and all together."""
     ctx_len, page = 1300, 16
@@ -135,10 +136,15 @@ def test_attention_ext_every_extra(K, dtype, nq, nkv, dk, dv, shared):
     for what, kw in variants.items():
         window = kw.pop("window", 0)
         want = TorchKernels().attention_ext(q, 8, nq, nkv, dk, dv, k_pool, v_pool, table, seq, pos, page, 0.3, window, ctx_len, **kw)
-        for batch in (None, step):
+        for batch in (None, step, "other tensor-core kernel"):
+            if batch == "other tensor-core kernel":   # sizes that the row-block-per-warp kernel takes: the split-part kernel as well
+                if not (dtype == "bfloat16" and not shared and dk in (64, 128) and dv in (64, 128)):
+                    continue
+                K.use_fa_attention_ext, batch = False, step
             got = K.attention_ext(q.cuda(), 8, nq, nkv, dk, dv, k_pool.cuda(), dev(v_pool), table.cuda(), seq.cuda(), pos.cuda(), page, 0.3, window,
                                   ctx_len, batch=batch, **{k: dev(v) for k, v in kw.items()})
             # (scores of ten and more, sums over up to 576 products: their exponentials carry a few 1e-7 of relative error each)
+            K.use_fa_attention_ext = True
             close(got, want, dtype, f"attention_ext {what} ({'generic' if batch is None else 'with the step'})",
                   scale=8.0 * max(1.0, dk / 64) ** 0.5 if dtype == "float32" else None)
 
