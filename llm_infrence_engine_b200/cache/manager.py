@@ -7,8 +7,10 @@ its own and every live request has one block table per group; the page with id 0
 * a state slot, from admission to the end: the row of every per-request array, and of every
   fixed-size state tensor (an architecture without such state still gets the slot);
 * in each group the pages that cover the positions it still has to read: all of them, or for a
-  windowed group those from ``length - window + 1`` on; pages that the window has passed go back
-  to the pool at once and their entry in the block table becomes the null page.
+  windowed group those from ``length - window + 1`` on (for a group that reads in runs of ``chunk``
+  positions, those from the start of the current run on); pages that the window has passed go back
+  to the pool at once and their entry in the block table becomes the null page. The pages of a
+  windowed group's first ``keep_first`` positions are never given back before the end.
 
 Pages come back when a request ends, is preempted, or a window has passed them, and are handed
 out again without being cleared: a position beyond a request's length is never read.
@@ -133,7 +135,8 @@ class CacheManager:
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.groups = list(groups)
-        self._windowed = any(g.window is not None for g in self.groups)
+        self._windowed = any(g.window is not None or g.chunk is not None for g in self.groups)
+        self._kept = [-(-g.keep_first // page_size) if g.window is not None else 0 for g in self.groups]  # leading pages never given back
         # pages can only be shared where a request's pages are all it has: one group, no window (a windowed group gives pages
         # back as it goes), and the caller says that no fixed-size state exists (``prefix_sharing`` is its promise)
         self.prefix_sharing = bool(prefix_sharing) and len(self.groups) == 1 and self.groups[0].window is None
@@ -239,24 +242,29 @@ class CacheManager:
 
     def _first_needed_page(self, group: int, context_len: int) -> int:
         """Index of the first page that a query at position >= context_len can still read."""
-        w = self.groups[group].window
-        if w is None:
-            return 0
-        return max(0, context_len - w + 1) // self.page_size
+        w, c = self.groups[group].window, self.groups[group].chunk
+        first = 0
+        if w is not None:
+            first = max(0, context_len - w + 1)
+        if c is not None:
+            first = max(first, context_len // c * c)
+        return first // self.page_size
 
     def _missing(self, held: "_Held", g: int, context_len: int, new_len: int) -> int:
         """Pages ``reserve`` would take from group ``g``'s pool, not counting those it gives back first. Pages from the
         first needed one up to the end of the table are always held, so only the table's growth counts."""
         want = -(-new_len // self.page_size)
         first = self._first_needed_page(g, context_len)
-        return max(0, want - max(len(held.tables[g]), first))
+        have = len(held.tables[g])
+        skipped = max(0, min(first, want) - max(have, self._kept[g]))   # table entries that stay null: passed, and not kept
+        return max(0, want - have - skipped)
 
     def _passed(self, held: "_Held", g: int, context_len: int) -> int:
         """Pages of group ``g`` that ``release_passed`` would give back."""
-        if self.groups[g].window is None:
+        if self.groups[g].window is None and self.groups[g].chunk is None:
             return 0
         first = min(self._first_needed_page(g, context_len), len(held.tables[g]))
-        return max(0, first - held.released[g])
+        return max(0, first - max(held.released[g], self._kept[g]))
 
     def pages_missing(self, req: Hashable, context_len: int, new_len: int) -> List[int]:
         """Per group, how many pages ``reserve`` would have to find in the pool beyond those it frees first."""
@@ -299,7 +307,7 @@ class CacheManager:
                 continue
             first = self._first_needed_page(g, context_len)
             while len(table) < want:
-                table.append(self.pools[g].allocate(req) if len(table) >= first else NULL_PAGE)
+                table.append(self.pools[g].allocate(req) if len(table) >= first or len(table) < self._kept[g] else NULL_PAGE)
             held.released[g] = max(held.released[g], min(first, len(table)))
             self._bump(held, g)
             self.max_blocks_per_seq = max(self.max_blocks_per_seq, len(table))
@@ -310,13 +318,13 @@ class CacheManager:
         held = self._held[req]
         n = 0
         for g in range(len(self.groups)):
-            if self.groups[g].window is None:
+            if self.groups[g].window is None and self.groups[g].chunk is None:
                 continue
             table = held.tables[g]
             upto = min(self._first_needed_page(g, context_len), len(table))
             if upto <= held.released[g]:
                 continue
-            for i in range(held.released[g], upto):
+            for i in range(max(held.released[g], self._kept[g]), upto):
                 if table[i] != NULL_PAGE:
                     self.pools[g].free(table[i], req)
                     table[i] = NULL_PAGE

@@ -323,3 +323,230 @@ class LuvutarConfig:
             o = self.layers[src].mixer
             if (o.kv_heads, o.dim, o.vdim) != (m.kv_heads, m.dim, m.vdim):
                 raise ConfigError(f"layers[{i}] reads the keys and values of layer {src}, whose head sizes differ")
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Zepalorn: a decoder whose config.json lists its layers one by one; a layer has one of three mixers and a gated
+# feed-forward, and may run on the weights of an earlier layer.
+
+def _opt_sub(d: Mapping[str, Any], key: str, where: str) -> Optional[Mapping[str, Any]]:
+    v = d.get(key)
+    if v is not None and not isinstance(v, Mapping):
+        raise ConfigError(f"config.json: {where}'{key}' must be an object")
+    return v
+
+
+@dataclass(frozen=True)
+class RotationConfig:
+    """``rot``: how many entries of a head turn, the base of the frequencies, and (under ``scaling``) how they are stretched."""
+
+    dims: int
+    base: float
+    factor: Optional[float] = None   # None: plain frequencies
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
+
+    @classmethod
+    def from_dict(cls, r: Mapping[str, Any], where: str) -> "RotationConfig":
+        dims = _pos_int(r, "dims", where)
+        if dims % 2:
+            raise ConfigError(f"config.json: {where}'dims' must be even, got {dims}")
+        base = _number(r, "base", where)
+        if not base > 1:
+            raise ConfigError(f"config.json: {where}'base' must be more than 1, got {base}")
+        sc = _opt_sub(r, "scaling", where)
+        if not sc:
+            return cls(dims, base)
+        w = where + "scaling."
+        factor, original = _number(sc, "factor", w), _number(sc, "original", w)
+        if not factor > 0 or not original > 0:
+            raise ConfigError(f"config.json: {w}'factor' and 'original' must be positive")
+        return cls(dims, base, factor, original, _number(sc, "fast", w), _number(sc, "slow", w))
+
+
+@dataclass(frozen=True)
+class MaskedAttentionConfig:
+    """Softmax attention over grouped heads. As the mixer ``attention``: plain projections, pairs ``(i, i + dims/2)`` turn, a
+    sliding window that keeps the first tokens. As the left half of ``parallel``: short convolutions, query/key norm,
+    neighbouring pairs turn, a soft cap on the scores, chunks."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    rot: Optional[RotationConfig] = None
+    mask_size: Optional[int] = None    # the window, or the chunk
+    keep_first: int = 0
+    chunked: bool = False
+    softcap: Optional[float] = None
+    conv: int = 0
+    qk_norm: bool = False
+    interleaved: bool = False
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str, side_by_side: bool = False) -> "MaskedAttentionConfig":
+        heads, kv_heads = _pos_int(m, "heads", where), _pos_int(m, "kv_heads", where)
+        if heads % kv_heads:
+            raise ConfigError(f"config.json: {where}{heads} heads cannot share {kv_heads} kv_heads")
+        dim = _pos_int(m, "dim", where)
+        rot = _opt_sub(m, "rot", where)
+        rot = RotationConfig.from_dict(rot, where + "rot.") if rot else None
+        if rot is not None and rot.dims > dim:
+            raise ConfigError(f"config.json: {where}rot.dims {rot.dims} is more than dim {dim}")
+        mask = _opt_sub(m, "mask", where)
+        size = _pos_int(mask, "size", where + "mask.") if mask else None
+        keep = 0
+        if mask and mask.get("keep_first") is not None:
+            keep = mask["keep_first"]
+            if isinstance(keep, bool) or not isinstance(keep, int) or keep < 0:
+                raise ConfigError(f"config.json: {where}mask.keep_first must be a count, got {keep!r}")
+            if side_by_side:
+                raise ConfigError(f"config.json: {where}mask.keep_first belongs to a window, not to chunks")
+        cap = _number(m, "softcap", where) if m.get("softcap") is not None else None
+        if cap is not None and not cap > 0:
+            raise ConfigError(f"config.json: {where}'softcap' must be positive, got {cap}")
+        conv = _pos_int(m, "conv", where) if m.get("conv") is not None else 0
+        if conv and not 2 <= conv <= 8:
+            raise ConfigError(f"config.json: {where}'conv' must be 2 to 8 taps, got {conv}")
+        if side_by_side and not conv:
+            raise ConfigError(f"config.json: {where}'conv' is missing")
+        return cls(heads, kv_heads, dim, _pos_int(m, "vdim", where) if "vdim" in m else dim, _number(m, "scale", where), rot, size, keep,
+                   chunked=side_by_side, softcap=cap, conv=conv, qk_norm=side_by_side, interleaved=side_by_side)
+
+
+@dataclass(frozen=True)
+class DeltaConfig:
+    """Mixer ``channel_delta``: the gated delta rule with a decay per head and key channel."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "DeltaConfig":
+        heads, kv_heads = _pos_int(m, "heads", where), _pos_int(m, "kv_heads", where)
+        if heads % kv_heads:
+            raise ConfigError(f"config.json: {where}{heads} heads cannot share {kv_heads} kv_heads")
+        dim, conv = _pos_int(m, "dim", where), _pos_int(m, "conv", where)
+        if dim > 256:
+            raise ConfigError(f"config.json: {where}'dim' {dim}: the delta rule is built for key sizes up to 256")
+        if not 2 <= conv <= 8:
+            raise ConfigError(f"config.json: {where}'conv' must be 2 to 8 taps, got {conv}")
+        return cls(heads, kv_heads, dim, _pos_int(m, "vdim", where), conv)
+
+
+@dataclass(frozen=True)
+class StateSpaceConfig:
+    """The right half of ``parallel``: a state-space mixer with one decay per head."""
+
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    norm_groups: int
+    conv: int
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "StateSpaceConfig":
+        c = cls(_pos_int(m, "heads", where), _pos_int(m, "vdim", where), _pos_int(m, "state", where), _pos_int(m, "groups", where),
+                _pos_int(m, "norm_groups", where), _pos_int(m, "conv", where))
+        if c.heads % c.groups:
+            raise ConfigError(f"config.json: {where}{c.heads} heads cannot share {c.groups} groups")
+        if (c.heads * c.vdim) % c.norm_groups:
+            raise ConfigError(f"config.json: {where}{c.heads * c.vdim} channels cannot be normed in {c.norm_groups} equal parts")
+        if c.state > 256:
+            raise ConfigError(f"config.json: {where}'state' {c.state}: the recurrence is built for state sizes up to 256")
+        if not 2 <= c.conv <= 8:
+            raise ConfigError(f"config.json: {where}'conv' must be 2 to 8 taps, got {c.conv}")
+        return c
+
+
+@dataclass(frozen=True)
+class ParallelConfig:
+    """Mixer ``parallel``: attention on the left, a state-space mixer on the right, both reading the same input."""
+
+    left: MaskedAttentionConfig
+    right: StateSpaceConfig
+
+    @classmethod
+    def from_dict(cls, m: Mapping[str, Any], where: str) -> "ParallelConfig":
+        return cls(MaskedAttentionConfig.from_dict(_sub(m, "left", where), where + "left.", side_by_side=True),
+                   StateSpaceConfig.from_dict(_sub(m, "right", where), where + "right."))
+
+
+@dataclass(frozen=True)
+class ZepalornLayerConfig:
+    kind: str                       # "channel_delta", "attention" or "parallel"
+    mixer: Any
+    ff: Optional[int]               # width of the gated feed-forward, None: the layer has none
+    ff_limit: float = 0.0
+    weights_of: Optional[int] = None  # the layer whose tensors this one runs on (with a cache and state of its own)
+
+
+@dataclass(frozen=True)
+class ZepalornConfig:
+    """The whole of a Zepalorn config.json: vocabulary, width, norm epsilon, the embedding's scale and the list of layers."""
+
+    architecture = "Zepalorn"
+
+    vocab: int
+    width: int
+    eps: float
+    embedding_scale: float
+    layers: tuple
+
+    @staticmethod
+    def _mixer(kind: str, m: Mapping[str, Any], where: str):
+        if kind == "channel_delta":
+            return DeltaConfig.from_dict(m, where)
+        if kind == "attention":
+            return MaskedAttentionConfig.from_dict(m, where)
+        if kind == "parallel":
+            return ParallelConfig.from_dict(m, where)
+        raise ConfigError(f"config.json: {where[:-6]}type {kind!r} is not one of ['attention', 'channel_delta', 'parallel']")
+
+    @classmethod
+    def from_dict(cls, d: Mapping[str, Any]) -> "ZepalornConfig":
+        if not isinstance(d.get("layers"), (list, tuple)) or not d["layers"]:
+            raise ConfigError("config.json: 'layers' must be a list with at least one layer")
+        layers = []
+        for i, layer in enumerate(d["layers"]):
+            where = f"layers[{i}]."
+            if not isinstance(layer, Mapping):
+                raise ConfigError(f"config.json: layers[{i}] must be an object")
+            kind = layer.get("type")
+            mixer = cls._mixer(kind, _sub(layer, "mixer", where), where + "mixer.")
+            mlp = layer.get("mlp")
+            ff, limit = None, 0.0
+            if mlp is not None:
+                if not isinstance(mlp, Mapping) or mlp.get("kind", "dense") != "dense":
+                    raise ConfigError(f"config.json: {where}mlp must be null or an object of kind 'dense'")
+                ff, limit = _pos_int(mlp, "ff", where + "mlp."), _number(mlp, "limit", where + "mlp.")
+                if not limit > 0:
+                    raise ConfigError(f"config.json: {where}mlp.limit must be positive, got {limit}")
+            src = layer.get("weights_of")
+            if src is not None and (isinstance(src, bool) or not isinstance(src, int) or src < 0):
+                raise ConfigError(f"config.json: {where}'weights_of' must be a layer index, got {src!r}")
+            layers.append(ZepalornLayerConfig(kind, mixer, ff, limit, src))
+        emb = _opt_sub(d, "embedding", "")
+        cfg = cls(_pos_int(d, "vocab", ""), _pos_int(d, "width", ""), _number(_sub(d, "norm", ""), "eps", "norm."),
+                  _number(emb, "scale", "embedding.") if emb and emb.get("scale") is not None else 1.0, tuple(layers))
+        cfg.validate()
+        return cfg
+
+    def validate(self) -> None:
+        if not self.eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.eps}")
+        for i, layer in enumerate(self.layers):
+            src = layer.weights_of
+            if src is None:
+                continue
+            if src >= i or self.layers[src].weights_of is not None:
+                raise ConfigError(f"layers[{i}].weights_of {src} must name an earlier layer with tensors of its own")
+            o = self.layers[src]
+            if (o.kind, o.mixer, o.ff, o.ff_limit) != (layer.kind, layer.mixer, layer.ff, layer.ff_limit):
+                raise ConfigError(f"layers[{i}] runs on the weights of layer {src}, but the rest of its entry differs from that layer's")

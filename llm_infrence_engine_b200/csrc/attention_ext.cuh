@@ -9,7 +9,10 @@
 //     table's last row beyond;
 //   * a sink: exp(sink[head]) joins the softmax's denominator once (it has no key and no value, and is not scaled);
 //   * an output gate: the result is multiplied by sigmoid(gate[n, head]) or sigmoid(gate[n, head * dv + i]);
-//   * a sliding window, as in the generic kernel.
+//   * a sliding window, as in the generic kernel; with `keep_first` the first tokens of the request stay visible after the
+//     window has passed them (at their true positions);
+//   * chunks: with `chunk` > 0 a position sees only keys of its own run of `chunk` positions, counted from the request's start;
+//   * a soft cap: score <- cap * tanh(score / cap), applied to the scaled score.
 //
 // Each extra is off when its pointer is null (or `temp_every` is 0). Sink and gate are applied where a (token, head) is
 // finished: in the block when there is one slice, in the merge kernel otherwise. With `slice_keys` > 0 the slices lie at
@@ -32,7 +35,17 @@ struct Extras {
     const float* sink;        // [nq] or null
     const void* gate;         // storage type of q; row n starts at gate + n * gate_stride
     int gate_stride, gate_mode;  // 0: none, 1: one number per head, 2: one per output element
+    int keep_first = 0;       // keys below this position are seen even when the window has passed them
+    int chunk = 0;            // > 0: only keys with floor(key / chunk) == floor(position / chunk) are seen
+    float softcap = 0.f;      // > 0: the scaled score s becomes softcap * tanh(s / softcap)
 };
+
+// First key that position p may see apart from the kept first tokens (window and chunk together).
+__device__ __forceinline__ int first_visible(int p, int window, const Extras& ex) {
+    int lo = window > 0 ? max(0, p - window + 1) : 0;
+    if (ex.chunk > 0) lo = max(lo, (p / ex.chunk) * ex.chunk);
+    return lo;
+}
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
 
@@ -85,16 +98,18 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_ext_kernel(
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
     const int p = positions[n];
-    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int lo = first_visible(p, window, ex);
+    const int kept = min(ex.keep_first, lo);   // keys [0, kept) are seen besides [lo, p]
     const int hi = p + 1;
     int start, end;
     if (slice_keys > 0) {
         start = split * slice_keys;
         end = min(hi, start + slice_keys);
     } else {
-        int per = (hi - lo + num_splits - 1) / num_splits;
+        const int from = kept > 0 ? 0 : lo;
+        int per = (hi - from + num_splits - 1) / num_splits;
         per = (per + 31) & ~31;
-        start = lo + split * per;
+        start = from + split * per;
         end = min(hi, start + per);
     }
     const int* table = block_table + (size_t)token_seq[n] * max_blocks;
@@ -124,9 +139,9 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_ext_kernel(
 
     constexpr int VN = Vec16<T>::N;
     for (int base = start + warp * 32; base < end; base += WARPS * 32) {
-        if (base + 32 <= lo) continue;  // (slices at fixed places only) every key of the chunk lies before the window
+        if (base + 32 <= lo && base >= kept) continue;  // every key of the chunk lies before the window and behind the kept ones
         const int key = base + lane;
-        const bool valid = key < end && key >= lo;
+        const bool valid = key < end && (key >= lo || key < kept);
         int row = 0;
         float s[GC];
 #pragma unroll
@@ -150,6 +165,10 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_ext_kernel(
 #pragma unroll
                     for (int g = 0; g < GC; ++g) s[g] = fmaf(qs[g * dkp + c], kf, s[g]);
                 }
+            }
+            if (ex.softcap > 0.f) {
+#pragma unroll
+                for (int g = 0; g < GC; ++g) s[g] = ex.softcap * tanhf(s[g] / ex.softcap);
             }
             if (ex.rel) {
                 const int dist = p - key;
@@ -176,7 +195,8 @@ __global__ void __launch_bounds__(WARPS * 32) paged_attn_ext_kernel(
 #pragma unroll
             for (int i = 0; i < DPL; ++i) acc[g][i] *= corr[g];
         const int count = min(32, end - base);
-        for (int j = max(0, lo - base); j < count; ++j) {
+        for (int j = 0; j < count; ++j) {
+            if (base + j < lo && base + j >= kept) continue;
             const int rj = __shfl_sync(0xffffffffu, row, j);
             const T* vr = v_base + (size_t)rj * v_row;
             float vv[DPL];

@@ -6,11 +6,12 @@ LLMIE_API int llmie_paged_attention_ext_f32(const float* q, int q_stride, const 
                                            int nq, int nkv, int dk, int dv, int page_size, float scale, int window, int num_splits,
                                            int slice_keys, float temp_coef, int temp_every, const float* rel, const int* rows_of,
                                            int n_rows_of, int rel_rows, const float* sink, const float* gate, int gate_stride, int gate_mode,
-                                           cudaStream_t s) {
+                                           int keep_first, int chunk, float softcap, cudaStream_t s) {
     attn_ext::Extras ex;
     ex.temp_coef = temp_coef; ex.temp_every = temp_every;
     ex.rel = rel; ex.rows_of = rows_of; ex.n_rows_of = n_rows_of; ex.rel_rows = rel_rows;
     ex.sink = sink; ex.gate = gate; ex.gate_stride = gate_stride; ex.gate_mode = gate_mode;
+    ex.keep_first = keep_first; ex.chunk = chunk; ex.softcap = softcap;
     return attn_ext::paged_attention_ext<float>(q, q_stride, k_pool, v_pool, block_table, max_blocks, token_seq, positions, out, scratch, N,
                                             nq, nkv, dk, dv, page_size, scale, window, num_splits, slice_keys, ex, s);
 }

@@ -14,22 +14,22 @@ LLMIE_API int llmie_set_pdl(int on) {
 }
 
 // ------------------------------------------------------------------------------------------------
-// x[n, :] = table[ids[n], :]  widened to float (the residual stream)
+// x[n, :] = table[ids[n], :] * scale  widened to float (the residual stream)
 template <typename T>
-__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int H) {
+__global__ void embed_kernel(const int* __restrict__ ids, const T* __restrict__ table, float* __restrict__ out, int H, float scale) {
     pdl_trigger();
     pdl_wait();
     const int n = blockIdx.x;
     const T* row = table + (size_t)ids[n] * H;
     float* o = out + (size_t)n * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
-LLMIE_API int llmie_embed(const int* ids, const void* table, float* out, int N, int H, int dtype, cudaStream_t s) {
+LLMIE_API int llmie_embed(const int* ids, const void* table, float* out, int N, int H, int dtype, float scale, cudaStream_t s) {
     if (N <= 0) return 0;
     const int threads = H >= 1024 ? 256 : 128;
-    if (dtype == DT_F32) return launch_kernel(embed_kernel<float>, dim3(N), dim3(threads), 0, s, ids, (const float*)table, out, H);
-    return launch_kernel(embed_kernel<bf16>, dim3(N), dim3(threads), 0, s, ids, (const bf16*)table, out, H);
+    if (dtype == DT_F32) return launch_kernel(embed_kernel<float>, dim3(N), dim3(threads), 0, s, ids, (const float*)table, out, H, scale);
+    return launch_kernel(embed_kernel<bf16>, dim3(N), dim3(threads), 0, s, ids, (const bf16*)table, out, H, scale);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -68,24 +68,24 @@ LLMIE_API int llmie_zero_fresh_state(float* state, long long row_floats, const i
 }
 
 // ------------------------------------------------------------------------------------------------
-// cos/sin[n, j] of the angle float(position[n]) * inv_freq[j], all in 32-bit
+// cos/sin[n, j] of the angle float(position[n]) * inv_freq[j], each times `mult`, all in 32-bit
 __global__ void rope_tables_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float* __restrict__ cos_out,
-                                   float* __restrict__ sin_out, int N, int half) {
+                                   float* __restrict__ sin_out, int N, int half, float mult) {
     pdl_trigger();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= N * half) return;
     const int n = i / half, j = i % half;
     const float ang = __int2float_rn(pos[n]) * inv_freq[j];
-    cos_out[i] = cosf(ang);
-    sin_out[i] = sinf(ang);
+    cos_out[i] = cosf(ang) * mult;
+    sin_out[i] = sinf(ang) * mult;
 }
 
-LLMIE_API int llmie_rope_tables(const int* pos, const float* inv_freq, float* cos_out, float* sin_out, int N, int half,
+LLMIE_API int llmie_rope_tables(const int* pos, const float* inv_freq, float* cos_out, float* sin_out, int N, int half, float mult,
                                 cudaStream_t s) {
     if (N <= 0) return 0;
     const int total = N * half;
-    return launch_kernel(rope_tables_kernel, dim3((total + 127) / 128), dim3(128), 0, s, pos, inv_freq, cos_out, sin_out, N, half);
+    return launch_kernel(rope_tables_kernel, dim3((total + 127) / 128), dim3(128), 0, s, pos, inv_freq, cos_out, sin_out, N, half, mult);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -538,5 +538,34 @@ LLMIE_API int llmie_act(void* in, void* out, long long total, int kind, int clea
     if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_kernel(act_kernel<float, float>, grid, dim3(256), 0, s, (float*)in, (float*)out, total, kind, clear_in);
     if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_kernel(act_kernel<float, bf16>, grid, dim3(256), 0, s, (float*)in, (bf16*)out, total, kind, clear_in);
     if (in_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_kernel(act_kernel<bf16, bf16>, grid, dim3(256), 0, s, (bf16*)in, (bf16*)out, total, kind, clear_in);
+    return LLMIE_ERR_BAD_ARGUMENT;
+}
+
+// ------------------------------------------------------------------------------------------------
+// A gated unit with bounded halves: for a fused gate/up projection [rows, 2 I] (gate first),
+//   g = min(gate, limit);  u = clamp(up, -limit, limit);  out = g * sigmoid(alpha * g) * (u + shift)
+// in 32-bit; `clear_in` zeroes what was read (a float32 accumulation buffer of a split-K product). grid = (rows, column blocks).
+template <typename TI, typename TO>
+__global__ void glu_clamped_kernel(TI* __restrict__ gu, TO* __restrict__ out, int I, int clear_in, float limit, float alpha, float shift) {
+    pdl_trigger();
+    pdl_wait();
+    const int i = blockIdx.y * blockDim.x + threadIdx.x;
+    if (i >= I) return;
+    TI* row = gu + (size_t)blockIdx.x * 2 * I;
+    float g = to_f32(row[i]), u = to_f32(row[I + i]);
+    if (clear_in) { row[i] = from_f32<TI>(0.f); row[I + i] = from_f32<TI>(0.f); }
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    out[(size_t)blockIdx.x * I + i] = from_f32<TO>(g / (1.0f + expf(-alpha * g)) * (u + shift));
+}
+
+LLMIE_API int llmie_glu_clamped(void* gu, void* out, int N, int I, int clear_in, float limit, float alpha, float shift, int in_dtype,
+                                int out_dtype, cudaStream_t s) {
+    if (N <= 0 || I <= 0) return 0;
+    if ((I + 127) / 128 > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    const dim3 grid(N, (I + 127) / 128);
+    if (in_dtype == DT_F32 && out_dtype == DT_F32) return launch_kernel(glu_clamped_kernel<float, float>, grid, dim3(128), 0, s, (float*)gu, (float*)out, I, clear_in, limit, alpha, shift);
+    if (in_dtype == DT_F32 && out_dtype == DT_BF16) return launch_kernel(glu_clamped_kernel<float, bf16>, grid, dim3(128), 0, s, (float*)gu, (bf16*)out, I, clear_in, limit, alpha, shift);
+    if (in_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_kernel(glu_clamped_kernel<bf16, bf16>, grid, dim3(128), 0, s, (bf16*)gu, (bf16*)out, I, clear_in, limit, alpha, shift);
     return LLMIE_ERR_BAD_ARGUMENT;
 }

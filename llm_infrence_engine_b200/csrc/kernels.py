@@ -68,6 +68,7 @@ class CudaKernels:
         # more rows); measured slower at 2,048 tokens (heads of 128: 311 -> 415 us): their registers leave one block per
         # multiprocessor where tiles of 32 rows leave two, and the kernel waits on its barriers, not on the keys
         self.attention_ext_tile_rows = 32
+        self.masked_attention_tensor_cores = False   # kept first tokens, chunks and soft caps on the tensor-core kernels too
         self.use_fa_attention_ext = True     # prompt portions with heads of 64 / 128: the kernel in which a warp owns 16 rows and all keys of a chunk
         self.head_matmul_library_rows = 64   # per-head products of latent attention: from this many rows on, one batched library product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
@@ -78,10 +79,13 @@ class CudaKernels:
         # An update of several residual streams waits here for the norm of the next sublayer, which updates, sums and
         # normalises in one pass: (streams, the sublayer's result, mix, out coefficients)
         self._pending_streams: Optional[tuple] = None
-        self._fresh_zero: Optional[torch.Tensor] = None   # the zeroed tensor that ``zeros_like_rows`` handed out last
+        # A sublayer's result whose layer norm is to be added into the residual stream waits here for the norm of the next
+        # sublayer, which adds and normalises in one pass: (stream, result, the post-norm's weight, eps)
+        self._pending_post: Optional[tuple] = None
+        self._fresh: list = []   # zeroed tensors of ``zeros_like_rows`` that nothing has been added into yet
         # ``zeros_like_rows`` hands out views of one float32 buffer that is zero between uses: the stream kernels that read a
         # sublayer's result out of it set it back to zero on their way (no fill kernel per sublayer)
-        self._zero_rows: Optional[torch.Tensor] = None
+        self._zero_bufs: list = []
         self._error_flag: Optional[torch.Tensor] = None
         self._acc_qkv: Optional[torch.Tensor] = None   # float32 sums of a decode step's q/k/v product, read by the attention kernel
         self._dirty_qkv: Optional[torch.Tensor] = None  # those sums while they still wait to be cleared
@@ -97,7 +101,9 @@ class CudaKernels:
                    "llmie_gemm_simt", "llmie_gemm_tc", "llmie_gateup_silu_tc", "llmie_qkv_rope_tc", "llmie_add_into", "llmie_attn_plan", "llmie_attn_tc_plan", "llmie_paged_attention_mma", "llmie_paged_attention_mma_acc", "llmie_paged_attention_tc", "llmie_paged_attention_f32", "llmie_paged_attention_bf16", "llmie_argmax", "llmie_sample",
                    "llmie_streams_expand", "llmie_streams_update", "llmie_streams_norm", "llmie_latent_prepare", "llmie_head_matmul",
                    "llmie_kv_store", "llmie_act", "llmie_paged_attention_ext_f32", "llmie_paged_attention_ext_bf16", "llmie_paged_attention_ext_mma",
-                   "llmie_attention_ext_mma_fits", "llmie_paged_attention_ext_fa", "llmie_attention_ext_fa_fits"):
+                   "llmie_attention_ext_mma_fits", "llmie_paged_attention_ext_fa", "llmie_attention_ext_fa_fits",
+                   "llmie_layernorm", "llmie_group_rmsnorm_gate", "llmie_dual_rmsnorm_mix", "llmie_glu_clamped", "llmie_qk_norm_rope_store",
+                   "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = None
@@ -125,9 +131,10 @@ class CudaKernels:
         is dropped, and the accumulation buffers, which every product assumes to be zero, are cleared."""
         self._pending_add = None
         self._pending_streams = None
-        self._fresh_zero = None
+        self._pending_post = None
+        self._fresh = []
         self._dirty_qkv = None
-        for t in [self._acc, self._acc_qkv, self._zero_rows, *self._retired_acc]:
+        for t in [self._acc, self._acc_qkv, *self._zero_bufs, *self._retired_acc]:
             if t is not None:
                 try:
                     t.zero_()
@@ -165,13 +172,13 @@ class CudaKernels:
         return _DT[t.dtype]
 
     # ------------------------------------------------------------------ kernels
-    def embed(self, token_ids, table):
+    def embed(self, token_ids, table, scale: float = 1.0):
         self._need(token_ids, "token_ids", torch.int32, 1)
         self._need(table, "table", None, 2)
         N, H = token_ids.shape[0], table.shape[1]
         out = torch.empty((N, H), dtype=torch.float32, device=table.device)
-        self._check(self.lib.llmie_embed(_ptr(token_ids), _ptr(table), _ptr(out), N, H, self._dt(table, "table"), self._stream()),
-                    "embed")
+        self._check(self.lib.llmie_embed(_ptr(token_ids), _ptr(table), _ptr(out), N, H, self._dt(table, "table"), ctypes.c_float(scale),
+                                        self._stream()), "embed")
         return out
 
     def feed_tokens(self, token_ids, source_rows, previous_tokens):
@@ -196,14 +203,14 @@ class CudaKernels:
             self._check(self.lib.llmie_zero_fresh_state(_ptr(state), ctypes.c_longlong(state.numel() // state.shape[0]), _ptr(seq_slots),
                                                         _ptr(seq_starts), _ptr(positions), R, self._stream()), "zero_fresh_state")
 
-    def rope_tables(self, positions, inv_freq):
+    def rope_tables(self, positions, inv_freq, mult: float = 1.0):
         self._need(positions, "positions", torch.int32, 1)
         self._need(inv_freq, "inv_freq", torch.float32, 1)
         N, half = positions.shape[0], inv_freq.shape[0]
         cos = torch.empty((N, half), dtype=torch.float32, device=positions.device)
         sin = torch.empty_like(cos)
-        self._check(self.lib.llmie_rope_tables(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), N, half, self._stream()),
-                    "rope_tables")
+        self._check(self.lib.llmie_rope_tables(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), N, half, ctypes.c_float(mult),
+                                              self._stream()), "rope_tables")
         return cos, sin
 
     def _norm(self, residual, delta, weight, eps, rows, out_dtype, what):
@@ -232,6 +239,7 @@ class CudaKernels:
         if self._pending_add is not None:
             target, y = self._pending_add
             self._pending_add = None
+            self._unfresh(target)
             self._check(self.lib.llmie_add_into(_ptr(target), _ptr(y), target.numel(), self._dt(y, "delta"), self._stream()), "add_into")
         if self._pending_streams is not None:
             xs, y, mix, coef_out = self._pending_streams
@@ -239,6 +247,10 @@ class CudaKernels:
             N, S, H = xs.shape
             self._check(self.lib.llmie_streams_update(_ptr(xs), _ptr(y), self._dt(y, "y"), int(self._clears(y)), _ptr(mix), _ptr(coef_out), N, S, H,
                                                       self._stream()), "streams_update")
+        if self._pending_post is not None:
+            x, y, w_post, eps = self._pending_post
+            self._pending_post = None
+            self._layernorm(x, y, w_post, None, eps, None, None, "post_norm_add")
 
     def _take_pending(self, residual, out_dtype):
         """The put-off addend for ``residual`` if there is one that the norm kernel can add on its way (same dtype as its output)."""
@@ -736,19 +748,42 @@ class CudaKernels:
         return out
 
     # ------------------------------------------------------------------ several residual streams
-    def zeros_like_rows(self, streams):
-        """A zeroed float32 ``[N, hidden]`` for a sublayer to add its result into (``streams`` is ``[N, S, hidden]``)."""
+    def zeros_like_rows(self, streams, index: int = 0):
+        """A zeroed float32 ``[N, hidden]`` for a sublayer to add its result into (``streams`` is ``[N, S, hidden]`` or
+        ``[N, hidden]``). ``index`` names one of several such buffers, for a part that needs more than one at a time."""
         N, H = streams.shape[0], streams.shape[-1]
-        if self._zero_rows is None or self._zero_rows.numel() < N * H or self._zero_rows.device != streams.device:
-            if self._zero_rows is not None:
-                self._retired_acc.append(self._zero_rows)   # a captured graph may still add into it and clear it
-            self._zero_rows = torch.zeros(max(N * H, 1 << 20), dtype=torch.float32, device=streams.device)
-        self._fresh_zero = self._zero_rows[: N * H].view(N, H)
-        return self._fresh_zero
+        while len(self._zero_bufs) <= index:
+            self._zero_bufs.append(None)
+        buf = self._zero_bufs[index]
+        if buf is None or buf.numel() < N * H or buf.device != streams.device:
+            if buf is not None:
+                self._retired_acc.append(buf)   # a captured graph may still add into it and clear it
+            buf = self._zero_bufs[index] = torch.zeros(max(N * H, 1 << 20), dtype=torch.float32, device=streams.device)
+        out = buf[: N * H].view(N, H)
+        self._fresh = [t for t in self._fresh if t.untyped_storage().data_ptr() != buf.untyped_storage().data_ptr()] + [out]
+        return out
+
+    def _is_fresh(self, y) -> bool:
+        return any(t is y for t in self._fresh)
+
+    def _unfresh(self, y) -> None:
+        self._fresh = [t for t in self._fresh if t is not y]
 
     def _clears(self, y) -> bool:
-        return (self._zero_rows is not None and y.dtype == torch.float32
-                and y.untyped_storage().data_ptr() == self._zero_rows.untyped_storage().data_ptr())
+        return y.dtype == torch.float32 and any(b is not None and y.untyped_storage().data_ptr() == b.untyped_storage().data_ptr()
+                                                for b in self._zero_bufs)
+
+    def take_result(self, y):
+        """What a sublayer left for a zeroed tensor of ``zeros_like_rows``: the tensor itself (float32 sums), or, where all it
+        was to receive is a library product that still waits to be added, that product (and the tensor stays zero)."""
+        if self._pending_add is not None and self._pending_add[0] is y and self._is_fresh(y):
+            out = self._pending_add[1]
+            self._pending_add = None
+            self._unfresh(y)
+            return out
+        self.flush()
+        self._unfresh(y)
+        return y
 
     def streams_expand(self, x, streams: int):
         self.flush()
@@ -774,11 +809,7 @@ class CudaKernels:
         streams (one pass does both) or until ``flush``. If ``y`` is the zeroed tensor of ``zeros_like_rows`` and all it
         holds is a library product that still waits to be added, the product itself is the update and ``y`` is never written."""
         self._check_streams(xs, mix, coef_out, "streams_update")
-        if self._pending_add is not None and self._pending_add[0] is y and self._fresh_zero is y:
-            y = self._pending_add[1]
-            self._pending_add = None
-        self.flush()
-        self._fresh_zero = None
+        y = self.take_result(y)
         self._need(y, "y", None, 2)
         if tuple(y.shape) != (xs.shape[0], xs.shape[2]):
             raise KernelError(f"streams_update: y is {list(y.shape)}, the streams are {list(xs.shape)}")
@@ -842,11 +873,13 @@ class CudaKernels:
 
     def attention_ext(self, q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions,
                       page_size, scale, window, max_context, temp=(0.0, 0), rel=None, rel_rows=None, sink=None, gate=None, gate_col=0,
-                      gate_per_head=False, batch=None, num_splits=None):
+                      gate_per_head=False, batch=None, num_splits=None, keep_first=0, chunk=0, softcap=0.0):
         """Paged attention with extras: the query heads are columns ``q_col ..`` of ``q``; ``v_pool=None`` reads the values out
         of the key rows (their first ``v_head_dim`` entries); ``temp=(coef, every)`` a query temperature by position;
         ``rel [rows, heads]`` with ``rel_rows`` (distance -> row) a bias by distance; ``sink [heads]`` joins the denominator;
-        ``gate`` (columns from ``gate_col`` of a tensor with the tokens' rows) an output gate per head or per element."""
+        ``gate`` (columns from ``gate_col`` of a tensor with the tokens' rows) an output gate per head or per element;
+        ``keep_first`` keys at the request's start stay visible when the ``window`` has passed them; ``chunk`` > 0 lets a position
+        see only the keys of its own run of ``chunk`` positions; ``softcap`` > 0 bounds the scaled scores by ``cap * tanh(s / cap)``."""
         self._need(q, "q", None, 2)
         dt = self._dt(q, "q")
         N = q.shape[0]
@@ -887,6 +920,11 @@ class CudaKernels:
         esize = q.element_size()
         max_rows = 0
         tensor_cores = dt == 1 and self.use_mma_attention_ext and batch is not None and (q_col * esize) % 16 == 0 and q.shape[1] % 8 == 0
+        masked = bool(keep_first or chunk or softcap)
+        if masked and not self.masked_attention_tensor_cores:
+            tensor_cores = False
+        if keep_first < 0 or chunk < 0 or softcap < 0 or (keep_first and not window):
+            raise KernelError("attention_ext: keep_first needs a window, and keep_first, chunk and softcap cannot be negative")
         if (tensor_cores and self.use_fa_attention_ext and batch.max_seq_len > 1
                 and self.lib.llmie_attention_ext_fa_fits(head_dim, v_head_dim, int(v_pool is not None), num_heads // num_kv_heads)):
             # steps with prompt portions, heads of 64 or 128: tiles of 64 rows, a warp to 16 rows and all of a chunk's keys
@@ -945,9 +983,234 @@ class CudaKernels:
                        ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel), _ptr(rel_rows), 0 if rel_rows is None else rel_rows.shape[0],
                        0 if rel is None else rel.shape[0], _ptr(sink),
                        ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1],
-                       gate_mode, self._stream()), "attention_ext")
+                       gate_mode, int(keep_first), int(chunk), ctypes.c_float(softcap), self._stream()), "attention_ext")
         if splits > 1:
             self.launches += 1
+        return out
+
+    # ------------------------------------------------------------------ layer norm before and after a sublayer
+    def _layernorm(self, x, y, w_post, w_pre, eps, rows, out_dtype, what):
+        self._need(x, "residual", torch.float32, 2)
+        N, H = x.shape
+        clear = False
+        y_dt = 0
+        if y is not None:
+            self._need(y, "y", None, 2)
+            y_dt = self._dt(y, "y")
+            if tuple(y.shape) != (N, H):
+                raise KernelError(f"{what}: the sublayer's result is {list(y.shape)}, the stream is {list(x.shape)}")
+            self._need(w_post, "w_post", torch.float32, 1)
+            if w_post.shape[0] != H:
+                raise KernelError(f"{what}: the post-norm's weight has {w_post.shape[0]} elements, rows have {H}")
+            clear = self._clears(y)
+        if H > 50000:
+            raise KernelError(f"{what}: rows of {H} elements do not fit the kernel's shared memory (at most 50000)")
+        out = None
+        out_dt = y_dt
+        n_out = N if rows is None else rows.shape[0]
+        if rows is not None:
+            self._need(rows, "rows", torch.int32, 1)
+        if w_pre is not None:
+            self._need(w_pre, "weight", torch.float32, 1)
+            if w_pre.shape[0] != H:
+                raise KernelError(f"{what}: weight has {w_pre.shape[0]} elements, rows have {H}")
+            out = torch.empty((n_out, H), dtype=out_dtype, device=x.device)
+            out_dt = _DT[out_dtype]
+            if y is None:
+                y_dt = 0
+            elif y_dt == 1 and out_dt == 0:
+                raise KernelError(f"{what}: a rounded result cannot feed a float32 norm")
+        elif y is None:
+            return None
+        self._check(self.lib.llmie_layernorm(_ptr(x), _ptr(y), y_dt, _ptr(w_post), int(clear), _ptr(w_pre), _ptr(out), out_dt, _ptr(rows), n_out, H,
+                                             ctypes.c_float(eps), self._stream()), what)
+        if clear and rows is not None:
+            y.zero_()   # only the chosen rows were read and cleared; the buffer must be zero for its next user
+            self.launches += 1
+        return out
+
+    def layernorm(self, residual, weight, eps, out_dtype, rows=None):
+        """``(x - mean) / sqrt(var + eps) * weight`` of the stream's rows (or of ``rows``), in ``out_dtype``. A sublayer's result
+        whose own layer norm still waits to be added into this stream (``post_norm_add``) is added by the same kernel."""
+        y = w_post = None
+        if (self._pending_post is not None and self._pending_post[0] is residual and self._pending_post[3] == eps
+                and self._pending_add is None and self._pending_streams is None):
+            _, y, w_post, _ = self._pending_post
+            self._pending_post = None
+            if rows is not None and y.dtype == torch.bfloat16 and out_dtype == torch.float32:
+                self._pending_post = (residual, y, w_post, eps)
+                y = w_post = None
+                self.flush()
+        else:
+            self.flush()
+        return self._layernorm(residual, y, w_post, weight, eps, rows, out_dtype, "layernorm")
+
+    def post_norm_add(self, residual, y, weight, eps):
+        """``residual += layernorm(y) * weight``: put off until the next ``layernorm`` of the same stream (one pass does both)
+        or until ``flush``. ``y`` is a zeroed tensor of ``zeros_like_rows`` that the sublayer added its result into."""
+        y = self.take_result(y)
+        self._pending_post = (residual, y, weight, float(eps))
+
+    def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype):
+        """Float32 rows ``x [N, C]`` normed by their root mean square in groups of ``group_size`` channels, with a gate read
+        from columns ``gate_col ..`` of ``gate``: ``gate_first`` multiplies by ``silu(gate)`` before the norm, otherwise by
+        ``sigmoid(gate)`` after it. ``weight`` has one entry per channel, or one per channel of a group (shared by all groups)."""
+        self._need(x, "x", torch.float32, 2)
+        N, C = x.shape
+        self._need(weight, "weight", torch.float32, 1)
+        if gate.dim() != 2 or gate.stride(1) != 1 or gate.shape[0] != N or gate_col + C > gate.shape[1] or gate.dtype != out_dtype:
+            raise KernelError("group_rmsnorm_gate: the gate must be rows of the output's type that hold a column for every channel")
+        if C % group_size or weight.shape[0] not in (C, group_size):
+            raise KernelError("group_rmsnorm_gate: the groups or the weight do not fit the channels")
+        out = torch.empty((N, C), dtype=out_dtype, device=x.device)
+        self._check(self.lib.llmie_group_rmsnorm_gate(_ptr(x), ctypes.c_void_p(gate.data_ptr() + gate_col * gate.element_size()), gate.stride(0),
+                                                      self._dt(gate, "gate"), _ptr(weight), weight.shape[0], _ptr(out), _DT[out_dtype], N, C,
+                                                      group_size, ctypes.c_float(eps), 0 if gate_first else 1, self._stream()), "group_rmsnorm_gate")
+        return out
+
+    def dual_rmsnorm_mix(self, a, b, weight_a, weight_b, eps, coef, add_to):
+        """``add_to += coef * (a / rms(a) * weight_a + b / rms(b) * weight_b)`` row by row (``add_to`` float32)."""
+        self.flush()
+        self._need(add_to, "add_to", torch.float32, 2)
+        N, H = add_to.shape
+        for name, t in (("a", a), ("b", b)):
+            self._need(t, name, None, 2)
+            if tuple(t.shape) != (N, H):
+                raise KernelError(f"dual_rmsnorm_mix: {name} is {list(t.shape)}, the target is {list(add_to.shape)}")
+        self._need(weight_a, "weight_a", torch.float32, 1)
+        self._need(weight_b, "weight_b", torch.float32, 1)
+        self._check(self.lib.llmie_dual_rmsnorm_mix(_ptr(a), self._dt(a, "a"), _ptr(b), self._dt(b, "b"), _ptr(weight_a), _ptr(weight_b), _ptr(add_to),
+                                                    N, H, ctypes.c_float(eps), ctypes.c_float(coef), 1, int(self._clears(a)), int(self._clears(b)), self._stream()),
+                    "dual_rmsnorm_mix")
+        self._unfresh(add_to)
+
+    def glu_clamped(self, gu, limit, alpha, shift, out_dtype=None):
+        """``g * sigmoid(alpha g) * (u + shift)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` of a fused gate/up
+        projection ``[rows, 2 I]`` (gate first); a transient float32 input is consumed and cleared."""
+        self._need(gu, "gate_up", None, 2)
+        if gu.shape[1] % 2:
+            raise KernelError("glu_clamped: the row must hold gate and up halves of equal width")
+        N, I = gu.shape[0], gu.shape[1] // 2
+        out = torch.empty((N, I), dtype=out_dtype or gu.dtype, device=gu.device)
+        self._check(self.lib.llmie_glu_clamped(_ptr(gu), _ptr(out), N, I, int(self._is_transient(gu)), ctypes.c_float(limit), ctypes.c_float(alpha),
+                                               ctypes.c_float(shift), self._dt(gu, "gate_up"), self._dt(out, "out"), self._stream()), "glu_clamped")
+        return out
+
+    # ------------------------------------------------------------------ heads normed and partly rotated on their way to the cache
+    def qk_norm_rope_store(self, z, num_heads, num_kv_heads, head_dim, v_head_dim, q_weight, k_weight, eps, cos, sin, rot_dims, interleaved,
+                           slot_mapping, k_pool, v_pool, page_size, write_kv=True):
+        """From rows ``z = [query heads | key heads | value heads]``: per query and key head an optional RMS norm with a weight,
+        then the rotation of its first ``rot_dims`` entries (pairs ``(i, i + rot_dims/2)``, or neighbours when ``interleaved``);
+        returns the query heads ``[N, heads * head_dim]`` and puts keys and values into the tokens' cache slots."""
+        self._need(z, "z", None, 2)
+        N = z.shape[0]
+        if z.shape[1] < (num_heads + num_kv_heads) * head_dim + num_kv_heads * v_head_dim:
+            raise KernelError("qk_norm_rope_store: the rows are too short for the heads")
+        if rot_dims:
+            self._need(cos, "cos", torch.float32, 2)
+            self._need(sin, "sin", torch.float32, 2)
+            if rot_dims % 2 or rot_dims > head_dim or tuple(cos.shape) != (N, rot_dims // 2) or tuple(sin.shape) != (N, rot_dims // 2):
+                raise KernelError("qk_norm_rope_store: cos and sin must be [tokens, rot_dims / 2] with rot_dims even and at most head_dim")
+        for name, t in (("q_weight", q_weight), ("k_weight", k_weight)):
+            if t is not None:
+                self._need(t, name, torch.float32, 1)
+                if t.shape[0] != head_dim:
+                    raise KernelError(f"qk_norm_rope_store: {name} needs one entry per element of a head")
+        if write_kv:
+            self._need(slot_mapping, "slot_mapping", torch.int32, 1)
+            for name, pool, d in (("k_pool", k_pool, head_dim), ("v_pool", v_pool, v_head_dim)):
+                self._need(pool, name, z.dtype, 4)
+                if tuple(pool.shape[1:]) != (num_kv_heads, page_size, d):
+                    raise KernelError(f"qk_norm_rope_store: {name} is {list(pool.shape)}, expected [pages, {num_kv_heads}, {page_size}, {d}]")
+        q = torch.empty((N, num_heads * head_dim), dtype=z.dtype, device=z.device)
+        self._check(self.lib.llmie_qk_norm_rope_store(_ptr(z), z.shape[1], _ptr(q), _ptr(q_weight), _ptr(k_weight), ctypes.c_float(eps), _ptr(cos if rot_dims else None),
+                                                      _ptr(sin if rot_dims else None), int(rot_dims), int(bool(interleaved)), _ptr(slot_mapping if write_kv else None),
+                                                      _ptr(k_pool if write_kv else None), _ptr(v_pool if write_kv else None), N, num_heads, num_kv_heads, head_dim,
+                                                      v_head_dim, page_size, int(bool(write_kv)), self._dt(z, "z"), self._stream()), "qk_norm_rope_store")
+        return q
+
+    # ------------------------------------------------------------------ mixers with a state of fixed size
+    def causal_conv(self, z, col, channels, weight, bias, state, batch, activation=None):
+        """A short causal convolution per channel over the rows of each request: ``y_t = act(bias + sum_j weight[:, j] u_(t - taps + 1 + j))``
+        for the columns ``col .. col + channels`` of ``z``; inputs from before the step come out of ``state [slots, taps - 1, channels]``
+        (float32), which is then moved on by the step's rows. ``batch`` is the step's context. Returns ``[N, channels]`` in z's type."""
+        self._need(z, "z", None, 2)
+        self._need(weight, "weight", torch.float32, 2)
+        self._need(state, "state", torch.float32, 3)
+        N = z.shape[0]
+        taps = weight.shape[1]
+        if weight.shape[0] != channels or col + channels > z.shape[1] or not 1 <= taps <= 8:
+            raise KernelError("causal_conv: the weight does not fit the columns (or has more than 8 taps)")
+        if tuple(state.shape[1:]) != (taps - 1, channels):
+            raise KernelError(f"causal_conv: state is {list(state.shape)}, expected [slots, {taps - 1}, {channels}]")
+        if bias is not None:
+            self._need(bias, "bias", torch.float32, 1)
+        if activation not in (None, "silu"):
+            raise KernelError(f"causal_conv: activation '{activation}' is not built")
+        out = torch.empty((N, channels), dtype=z.dtype, device=z.device)
+        self._check(self.lib.llmie_causal_conv(ctypes.c_void_p(z.data_ptr() + col * z.element_size()), z.shape[1], channels, _ptr(weight), _ptr(bias),
+                                               _ptr(state), _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(out), channels, taps,
+                                               1 if activation == "silu" else 0, batch.num_seqs, batch.max_seq_len, self._dt(z, "z"), self._stream()),
+                    "causal_conv")
+        return out
+
+    def delta_rule(self, qkv, num_heads, num_kv_heads, head_dim, v_head_dim, a, b, b_col, A_log, dt_bias, state, batch, unit_eps=1e-6):
+        """The gated delta rule with a decay per key channel over the rows of each request, from ``state [slots, heads, head_dim, v_head_dim]``:
+        ``qkv = [q: kv_heads x head_dim | k: the same | v: heads x v_head_dim]`` (after convolution and activation), ``a [N, heads * head_dim]``
+        the decay's logits, ``b`` (columns from ``b_col``) the logits of beta. Returns float32 ``[N, heads * v_head_dim]``."""
+        self._need(qkv, "qkv", None, 2)
+        self._need(a, "a", qkv.dtype, 2)
+        self._need(state, "state", torch.float32, 4)
+        N = qkv.shape[0]
+        H, G, D, DV = num_heads, num_kv_heads, head_dim, v_head_dim
+        if qkv.shape[1] < 2 * G * D + H * DV or a.shape[1] != H * D or H % G or D > 256:
+            raise KernelError("delta_rule: the rows do not fit the head sizes (head_dim at most 256)")
+        if b.dim() != 2 or b.stride(1) != 1 or b.dtype != qkv.dtype or b_col + H > b.shape[1]:
+            raise KernelError("delta_rule: the beta logits must be columns of rows of the same type")
+        if tuple(state.shape[1:]) != (H, D, DV):
+            raise KernelError(f"delta_rule: state is {list(state.shape)}, expected [slots, {H}, {D}, {DV}]")
+        self._need(A_log, "A_log", torch.float32, 1)
+        self._need(dt_bias, "dt_bias", torch.float32, 1)
+        dev = qkv.device
+        work = torch.empty((N, 2 * G * D + G + H * D + H), dtype=torch.float32, device=dev)
+        flat = work.view(-1)
+        o = 0
+        pieces = []
+        for n in (N * G * D, N * G * D, N * G, N * H * D, N * H):
+            pieces.append(flat[o:o + n])
+            o += n
+        qn, kn, kq, decay, beta = pieces
+        dt = self._dt(qkv, "qkv")
+        self._check(self.lib.llmie_delta_prepare(_ptr(qkv), qkv.shape[1], 0, G * D, _ptr(a), a.shape[1], ctypes.c_void_p(b.data_ptr() + b_col * b.element_size()),
+                                                 b.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(qn), _ptr(kn), _ptr(kq), _ptr(decay), _ptr(beta), N, H, G, D,
+                                                 ctypes.c_float(D ** -0.5), ctypes.c_float(unit_eps), dt, self._stream()), "delta_rule (prepare)")
+        out = torch.empty((N, H * DV), dtype=torch.float32, device=dev)
+        self._check(self.lib.llmie_delta_scan(_ptr(qkv), qkv.shape[1], 2 * G * D, _ptr(qn), _ptr(kn), _ptr(kq), _ptr(decay), _ptr(beta), _ptr(state),
+                                              _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(out), H, G, D, DV, batch.num_seqs, dt, self._stream()),
+                    "delta_rule (scan)")
+        return out
+
+    def ssm_scan(self, xbc, num_heads, groups, state_size, v_head_dim, dt, dt_col, A_log, dt_bias, skip, state, batch):
+        """The state-space recurrence with one decay per head over the rows of each request, from ``state [slots, heads, state_size,
+        v_head_dim]``: ``xbc = [x: heads x v_head_dim | B: groups x state_size | C: the same]`` (after convolution and activation), ``dt``
+        (columns from ``dt_col``) the step sizes' logits. Returns float32 ``[N, heads * v_head_dim]``."""
+        self._need(xbc, "xbc", None, 2)
+        self._need(state, "state", torch.float32, 4)
+        H, G, NS, DV = num_heads, groups, state_size, v_head_dim
+        if xbc.shape[1] != H * DV + 2 * G * NS or H % G or NS > 256:
+            raise KernelError("ssm_scan: the rows do not fit the head sizes (state size at most 256)")
+        if dt.dim() != 2 or dt.stride(1) != 1 or dt.dtype != xbc.dtype or dt_col + H > dt.shape[1]:
+            raise KernelError("ssm_scan: the step sizes must be columns of rows of the same type")
+        if tuple(state.shape[1:]) != (H, NS, DV):
+            raise KernelError(f"ssm_scan: state is {list(state.shape)}, expected [slots, {H}, {NS}, {DV}]")
+        for name, t in (("A_log", A_log), ("dt_bias", dt_bias), ("skip", skip)):
+            self._need(t, name, torch.float32, 1)
+            if t.shape[0] != H:
+                raise KernelError(f"ssm_scan: {name} needs one entry per head")
+        out = torch.empty((xbc.shape[0], H * DV), dtype=torch.float32, device=xbc.device)
+        self._check(self.lib.llmie_ssm_scan(_ptr(xbc), xbc.shape[1], 0, H * DV, H * DV + G * NS, ctypes.c_void_p(dt.data_ptr() + dt_col * dt.element_size()),
+                                            dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(skip), _ptr(state), _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots),
+                                            _ptr(out), H, G, NS, DV, batch.num_seqs, self._dt(xbc, "xbc"), self._stream()), "ssm_scan")
         return out
 
     # ------------------------------------------------------------------ latent attention

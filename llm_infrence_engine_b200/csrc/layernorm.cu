@@ -1,0 +1,174 @@
+// Layer norm with a weight and no bias, for blocks that norm a sublayer's input AND its result:
+//   x <- x + LN_post(y);  h = LN_pre(x)
+// One kernel does either half or both, one block per row, the row in shared memory between the passes. Mean, variance
+// (the mean of the squared deviations, taken in a second pass) and the scaling are 32-bit. Also here: the root-mean-square
+// norm over groups of a row with a gate, and the mean of several rows each divided by its root mean square.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf(-x)); }
+
+// rows == nullptr: r = blockIdx.x and the updated x is stored; rows != nullptr: r = rows[blockIdx.x], nothing of x is stored.
+// y (of type TY, or null): the sublayer's result whose layer norm (weight w_post) is added to x first; with clear_y the row of
+// y is set to zero behind the read (it is then a float buffer that the next sublayer adds into).
+// w_pre (or null): out[blockIdx.x] = LN(x) * w_pre in type TO.
+template <typename TY, typename TO>
+__global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, const float* __restrict__ w_post, int clear_y,
+                                 const float* __restrict__ w_pre, TO* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    extern __shared__ __align__(16) float ln_buf[];   // H floats of the row, 36 for the reductions
+    float* scratch = ln_buf + H;
+    pdl_trigger();
+    pdl_wait();
+    const int r = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* xr = x + (size_t)r * H;
+    if (y) {
+        TY* yr = y + (size_t)r * H;
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = to_f32(yr[i]);
+            ln_buf[i] = v;
+            sum += v;
+            if (clear_y) yr[i] = from_f32<TY>(0.f);
+        }
+        const float mean = block_sum(sum, scratch) / (float)H;
+        float sq = 0.f;
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float d = ln_buf[i] - mean;
+            sq = fmaf(d, d, sq);
+        }
+        const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            const float v = xr[i] + (ln_buf[i] - mean) * rstd * w_post[i];
+            ln_buf[i] = v;
+            if (!rows) xr[i] = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) ln_buf[i] = xr[i];
+    }
+    if (!w_pre) return;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) sum += ln_buf[i];   // a thread reads back what it wrote itself
+    const float mean = block_sum(sum, scratch) / (float)H;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float d = ln_buf[i] - mean;
+        sq = fmaf(d, d, sq);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+    TO* o = out + (size_t)blockIdx.x * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((ln_buf[i] - mean) * rstd * w_pre[i]);
+}
+
+template <typename TY, typename TO>
+int launch_layernorm(float* x, void* y, const float* w_post, int clear_y, const float* w_pre, void* out, const int* rows, int n_out,
+                     int H, float eps, cudaStream_t s) {
+    const size_t smem = (size_t)(H + 36) * sizeof(float);
+    int threads = 32;
+    while (threads < 512 && threads * 4 <= H) threads *= 2;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_kernel(layernorm_kernel<TY, TO>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, (TO*)out, rows, H, eps);
+}
+
+// Root-mean-square norm over groups of `gs` consecutive channels, with a gate, one block per (row, group):
+//   mode 0: v = x * silu(gate);            out = v / rms(v) * w                     (the gate comes before the norm)
+//   mode 1: out = x / rms(x) * w * sigmoid(gate)                                    (the gate comes after it)
+// w has w_len entries and channel c uses w[c % w_len] (one weight per channel, or one vector shared by all groups).
+template <typename TG, typename TO>
+__global__ void group_rmsnorm_gate_kernel(const float* __restrict__ x, const TG* __restrict__ gate, int gate_stride,
+                                          const float* __restrict__ w, int w_len, TO* __restrict__ out, int C, int gs, float eps, int mode) {
+    __shared__ float scratch[36];
+    pdl_trigger();
+    pdl_wait();
+    const int n = blockIdx.x, c0 = blockIdx.y * gs;
+    const float* xr = x + (size_t)n * C + c0;
+    const TG* gr = gate + (size_t)n * gate_stride + c0;
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        float v = xr[i];
+        if (mode == 0) { const float z = to_f32(gr[i]); v *= z / (1.0f + expf(-z)); }
+        sq = fmaf(v, v, sq);
+    }
+    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)gs + eps);
+    TO* o = out + (size_t)n * C + c0;
+    for (int i = threadIdx.x; i < gs; i += blockDim.x) {
+        float v = xr[i];
+        const float z = to_f32(gr[i]);
+        if (mode == 0) v *= z / (1.0f + expf(-z));
+        v = v * rstd * w[(c0 + i) % w_len];
+        if (mode == 1) v *= sigmoid_f(z);
+        o[i] = from_f32<TO>(v);
+    }
+}
+
+// y[n] (+)= coef * (a[n] / rms(a[n]) * wa + b[n] / rms(b[n]) * wb): two sublayer results of one input, each normed by itself,
+// then their mean. One block per row. The inputs may be float sums or rounded rows of a library product; with clear_a / clear_b
+// an input is set to zero behind the read (a float buffer that the next sublayer adds into).
+template <typename TA, typename TB>
+__global__ void dual_rmsnorm_mix_kernel(TA* __restrict__ a, TB* __restrict__ b, const float* __restrict__ wa,
+                                        const float* __restrict__ wb, float* __restrict__ y, int H, float eps, float coef, int accumulate,
+                                        int clear_a, int clear_b) {
+    __shared__ float scratch[36];
+    pdl_trigger();
+    pdl_wait();
+    const size_t off = (size_t)blockIdx.x * H;
+    float sa = 0.f, sb = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float va = to_f32(a[off + i]), vb = to_f32(b[off + i]);
+        sa = fmaf(va, va, sa);
+        sb = fmaf(vb, vb, sb);
+    }
+    const float ra = 1.0f / sqrtf(block_sum(sa, scratch) / (float)H + eps);
+    const float rb = 1.0f / sqrtf(block_sum(sb, scratch) / (float)H + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = coef * (to_f32(a[off + i]) * ra * wa[i] + to_f32(b[off + i]) * rb * wb[i]);
+        if (clear_a) a[off + i] = from_f32<TA>(0.f);
+        if (clear_b) b[off + i] = from_f32<TB>(0.f);
+        y[off + i] = accumulate ? y[off + i] + v : v;
+    }
+}
+
+}  // namespace
+
+LLMIE_API int llmie_layernorm(float* x, void* y, int y_dtype, const float* w_post, int clear_y, const float* w_pre, void* out,
+                              int out_dtype, const int* rows, int n_out, int H, float eps, cudaStream_t s) {
+    if (n_out <= 0) return 0;
+    if (H <= 0 || (size_t)(H + 36) * sizeof(float) > 200 * 1024 || (y && !w_post) || (w_pre && !out)) return LLMIE_ERR_BAD_ARGUMENT;
+    if (y_dtype == DT_F32 && out_dtype == DT_F32) return launch_layernorm<float, float>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
+    if (y_dtype == DT_F32 && out_dtype == DT_BF16) return launch_layernorm<float, bf16>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
+    if (y_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_layernorm<bf16, bf16>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
+    return LLMIE_ERR_BAD_ARGUMENT;
+}
+
+LLMIE_API int llmie_group_rmsnorm_gate(const float* x, const void* gate, int gate_stride, int gate_dtype, const float* w, int w_len,
+                                       void* out, int out_dtype, int N, int C, int gs, float eps, int mode, cudaStream_t s) {
+    if (N <= 0) return 0;
+    if (C <= 0 || gs <= 0 || C % gs || w_len <= 0 || C / gs > 65535 || mode < 0 || mode > 1) return LLMIE_ERR_BAD_ARGUMENT;
+    int threads = 32;
+    while (threads < 256 && threads * 2 <= gs) threads *= 2;
+    const dim3 grid(N, C / gs);
+#define LLMIE_GRG(TG, TO) return launch_kernel(group_rmsnorm_gate_kernel<TG, TO>, grid, dim3(threads), 0, s, x, (const TG*)gate, gate_stride, w, w_len, \
+                                               (TO*)out, C, gs, eps, mode)
+    if (gate_dtype == DT_F32 && out_dtype == DT_F32) LLMIE_GRG(float, float);
+    if (gate_dtype == DT_BF16 && out_dtype == DT_BF16) LLMIE_GRG(bf16, bf16);
+#undef LLMIE_GRG
+    return LLMIE_ERR_BAD_ARGUMENT;
+}
+
+LLMIE_API int llmie_dual_rmsnorm_mix(void* a, int a_dtype, void* b, int b_dtype, const float* wa, const float* wb, float* y, int N, int H,
+                                     float eps, float coef, int accumulate, int clear_a, int clear_b, cudaStream_t s) {
+    if (N <= 0) return 0;
+    if (H <= 0) return LLMIE_ERR_BAD_ARGUMENT;
+    int threads = 32;
+    while (threads < 512 && threads * 4 <= H) threads *= 2;
+#define LLMIE_DUAL(TA, TB) return launch_kernel(dual_rmsnorm_mix_kernel<TA, TB>, dim3(N), dim3(threads), 0, s, (TA*)a, (TB*)b, wa, wb, y, H, eps, coef, \
+                                                accumulate, clear_a, clear_b)
+    if (a_dtype == DT_F32 && b_dtype == DT_F32) LLMIE_DUAL(float, float);
+    if (a_dtype == DT_F32 && b_dtype == DT_BF16) LLMIE_DUAL(float, bf16);
+    if (a_dtype == DT_BF16 && b_dtype == DT_F32) LLMIE_DUAL(bf16, float);
+    if (a_dtype == DT_BF16 && b_dtype == DT_BF16) LLMIE_DUAL(bf16, bf16);
+#undef LLMIE_DUAL
+    return LLMIE_ERR_BAD_ARGUMENT;
+}

@@ -25,7 +25,7 @@ from ..sampling.sampler import Sampler, SamplingParams
 from ..weights.loader import load_weights
 from .request import GenerationResult, Request, StepRecord
 from .scheduler import Scheduler, StepPlan
-from .step import ModelRunner, StepEntry, group_layout
+from .step import ModelRunner, StepEntry, group_layout, has_fixed_state
 
 _TORCH_DTYPE = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -40,9 +40,10 @@ def build_runner(folder: Union[str, Path], config: EngineConfig, kernels=None):
     spec = build_model_spec(read_config_json(folder))
     dtype = _TORCH_DTYPE[config.dtype]
     load_weights(spec, folder, dtype, config.device)
-    groups, of_entry = group_layout(spec.cache_specs())
+    specs = spec.cache_specs()
+    groups, of_entry = group_layout(specs)
     num_pages = config.pool_blocks()
-    stateless = all(e is not None for e in of_entry)  # every cache entry is paged: no fixed-size state to snapshot
+    stateless = all(e is not None for e in of_entry) and not has_fixed_state(specs)  # every cache entry is paged: no fixed-size state to snapshot
     cache = CacheManager(groups, num_pages, config.block_size, config.max_seqs, prefix_sharing=config.prefix_cache and stateless)
     runner = ModelRunner(spec, kernels, cache, of_entry, dtype, config.device, num_pages, config.block_size, config.max_seqs,
                          config.max_len, config.cuda_graphs)

@@ -21,7 +21,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
-from ..cache.spec import NULL_PAGE, FixedStateSpec, PagedKVSpec
+from ..cache.spec import NULL_PAGE, FixedStateSpec, PagedKVSpec, flatten_specs
 from ..models.spec import ModelSpec
 
 
@@ -107,19 +107,28 @@ class ModelRunner:
         self.bindings: List[object] = []
         self.kv_bytes_per_token = 0
         specs = spec.cache_specs()
-        for entry, cs in enumerate(specs):
+        self.state_bindings: List[StateBinding] = []   # every fixed-size state of the model, wherever it is bound
+
+        def bind(entry, cs, group):
+            """The binding of one spec; a tuple of specs (a mixer that asks for several things) gives a tuple of bindings."""
+            if isinstance(cs, (tuple, list)):
+                return tuple(bind(entry, c, g) for c, g in zip(cs, group))
             if isinstance(cs, PagedKVSpec):
                 v_dim = cs.head_dim if cs.v_head_dim is None else cs.v_head_dim
                 k = torch.zeros((num_pages, cs.num_kv_heads, page_size, cs.head_dim), dtype=dtype, device=self.device)
                 v = torch.zeros((num_pages, cs.num_kv_heads, page_size, v_dim), dtype=dtype, device=self.device) if v_dim else None
-                self.bindings.append(PagedKVBinding(group_of_entry[entry], k, v))
                 self.kv_bytes_per_token += cs.num_kv_heads * (cs.head_dim + v_dim) * k.element_size()
-            elif isinstance(cs, FixedStateSpec):
-                self.bindings.append(StateBinding(torch.zeros((max_seqs + 1,) + tuple(cs.shape), dtype=torch.float32, device=self.device)))
-            elif cs is None:
-                self.bindings.append(None)
-            else:
-                raise TypeError(f"cache entry {entry} has a spec of unknown kind {type(cs).__name__}")
+                return PagedKVBinding(group, k, v)
+            if isinstance(cs, FixedStateSpec):
+                b = StateBinding(torch.zeros((max_seqs + 1,) + tuple(cs.shape), dtype=torch.float32, device=self.device))
+                self.state_bindings.append(b)
+                return b
+            if cs is None:
+                return None
+            raise TypeError(f"cache entry {entry} has a spec of unknown kind {type(cs).__name__}")
+
+        for entry, cs in enumerate(specs):
+            self.bindings.append(bind(entry, cs, group_of_entry[entry]))
         # Block tables live on the device, one row per state slot (plus a last row of null pages that padding
         # rows of a captured graph point at); a row is sent again only when the request's table has changed.
         self.max_blocks = max(1, -(-max_len // page_size))
@@ -382,16 +391,15 @@ class ModelRunner:
 
     def _forward(self, ctx: StepContext, logit_rows: torch.Tensor) -> Optional[torch.Tensor]:
         spec = self.spec
-        for b in self.bindings:   # a request's fixed-size state starts from zero: decided on the device, so captured steps do it too
-            if isinstance(b, StateBinding):
-                self.K.zero_fresh_state(b.state, ctx.seq_slots, ctx.seq_starts_dev, ctx.positions)
+        for b in self.state_bindings:   # a request's fixed-size state starts from zero: decided on the device, so captured steps do it too
+            self.K.zero_fresh_state(b.state, ctx.seq_slots, ctx.seq_starts_dev, ctx.positions)
         residual = spec.embedding.forward(ctx)
         if spec.streams is not None:   # several residual streams: the layers work on [N, streams, hidden]
             residual = spec.streams.expand(ctx, residual)
         for call in spec.schedule:
             b = self.bindings[call.cache]
-            if b is not None and b.write != call.write:
-                b = type(b)(**{**b.__dict__, "write": call.write})
+            if not call.write:
+                b = _read_only(b)
             spec.layers[call.layer].forward(ctx, residual, b)
         if logit_rows.numel() == 0:
             if hasattr(self.K, "flush"):
@@ -418,15 +426,33 @@ class ModelRunner:
         return n
 
 
+def _read_only(b):
+    """The same binding (or tuple of bindings) for a call of the running order that reads a cache entry without writing it."""
+    if b is None:
+        return None
+    if isinstance(b, tuple):
+        return tuple(_read_only(x) for x in b)
+    return b if not b.write else type(b)(**{**b.__dict__, "write": False})
+
+
 def group_layout(specs: Sequence[object]):
-    """Distinct ``PagedKVSpec`` values in order of appearance, and for every cache entry its group (None if not paged)."""
+    """Distinct ``PagedKVSpec`` values in order of appearance, and for every cache entry its group (None if not paged; for an
+    entry that is a tuple of specs, a tuple of the same shape)."""
     groups: List[PagedKVSpec] = []
-    of_entry: List[Optional[int]] = []
-    for cs in specs:
+
+    def place(cs):
+        if isinstance(cs, (tuple, list)):
+            return tuple(place(c) for c in cs)
         if isinstance(cs, PagedKVSpec):
             if cs not in groups:
                 groups.append(cs)
-            of_entry.append(groups.index(cs))
-        else:
-            of_entry.append(None)
+            return groups.index(cs)
+        return None
+
+    of_entry = [place(cs) for cs in specs]
     return groups, of_entry
+
+
+def has_fixed_state(specs: Sequence[object]) -> bool:
+    """True if any cache entry holds a state of fixed size (which pages cannot stand in for, so prefixes cannot be shared)."""
+    return any(isinstance(c, FixedStateSpec) for cs in specs for c in flatten_specs(cs))

@@ -36,6 +36,10 @@ INIT_SMALL = "small"        # N(0, 0.1): weights kept around zero, biases by dis
 INIT_SHARE = "share"        # 1 / n + N(0, 0.05) for a vector of n: how much of each residual stream a sublayer reads
 INIT_ONES = "ones"          # 1 + N(0, 0.05): how much of a sublayer's result each residual stream takes
 INIT_EYE = "eye"            # identity + N(0, 0.05): how the residual streams mix
+INIT_LOG_RATE = "log_rate"  # ln U(0.5, 4): the logarithm of a decay rate
+INIT_STEP_BIAS = "step_bias"  # softplus^-1 of a step size drawn log-uniformly from 0.01 to 0.3
+INIT_TAPS = "taps"          # N(0, 0.3): the few taps of a short convolution
+INIT_PROJ = "projection"    # N(0, 1 / sqrt(columns)): a matrix whose product keeps its input's scale
 
 ANY = -1  # a dimension of a Source's shape that the checkpoint decides (the part reads it off the tensor it is given)
 
@@ -63,8 +67,8 @@ class ParamSpec:
 
     @property
     def shape(self) -> Tuple[int, ...]:
-        first = self.sources[0].shape
-        return (sum(s.shape[0] for s in self.sources),) + tuple(first[1:])
+        first = self.sources[0].drawn_shape()
+        return (sum(s.drawn_shape()[0] for s in self.sources),) + tuple(first[1:])
 
 
 class Part:

@@ -33,3 +33,38 @@ class PreNormBlock(Part):
         self.mixer.forward(ctx, self.norm1.norm(ctx, residual), cache, residual)
         if self.ff is not None:   # a layer may be a mixer alone
             self.ff.forward(ctx, self.norm2.norm(ctx, residual), residual)
+
+
+class SandwichBlock(Part):
+    """``x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x)))``: a norm before every sublayer and another on its result.
+
+    A sublayer adds its result into a zeroed tensor exactly as it would add into the residual stream (so any mixer or
+    feed-forward of the package fits); the closing norm then adds the normed result into the stream. The closing norms have
+    ``add_normed(ctx, residual, y)``.
+    """
+
+    graph_safe = True
+
+    def __init__(self, norm1: Norm, mixer: Mixer, norm1b: Norm, norm2: Optional[Norm] = None, ff: Optional[FeedForward] = None,
+                 norm2b: Optional[Norm] = None):
+        if (norm2 is None) != (ff is None) or (norm2b is None) != (ff is None):
+            raise ValueError("a feed-forward comes with its two norms, or none of the three is there")
+        self.norm1, self.mixer, self.norm1b, self.norm2, self.ff, self.norm2b = norm1, mixer, norm1b, norm2, ff, norm2b
+
+    def children(self) -> Sequence[Part]:
+        return tuple(p for p in (self.norm1, self.mixer, self.norm1b, self.norm2, self.ff, self.norm2b) if p is not None)
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx, residual: torch.Tensor, cache) -> None:
+        K = ctx.K
+        h = self.norm1.norm(ctx, residual)
+        y = K.zeros_like_rows(residual)
+        self.mixer.forward(ctx, h, cache, y)
+        self.norm1b.add_normed(ctx, residual, y)
+        if self.ff is not None:
+            h = self.norm2.norm(ctx, residual)
+            y = K.zeros_like_rows(residual)
+            self.ff.forward(ctx, h, y)
+            self.norm2b.add_normed(ctx, residual, y)

@@ -9,19 +9,22 @@ from .base import MATRIX, ParamSpec, Part, Source
 
 
 class TokenEmbedding(Part):
-    """``x = table[token]`` with no scaling (src/miniserve/model.py:229), widened into the 32-bit residual stream."""
+    """``x = table[token] * scale`` (the reference has no scaling, src/miniserve/model.py:229), widened into the 32-bit
+    residual stream; the product is taken in 32-bit."""
 
     graph_safe = True
 
-    def __init__(self, vocab: int, hidden: int, name: str):
-        self.vocab, self.hidden, self.name = vocab, hidden, name
+    def __init__(self, vocab: int, hidden: int, name: str, scale: float = 1.0):
+        self.vocab, self.hidden, self.name, self.scale = vocab, hidden, name, float(scale)
         self.table: Optional[torch.Tensor] = None
 
     def params(self) -> Dict[str, ParamSpec]:
         return {"table": ParamSpec((Source(self.name, (self.vocab, self.hidden)),), MATRIX)}
 
     def forward(self, ctx) -> torch.Tensor:
-        return ctx.K.embed(ctx.token_ids, self.table)
+        if self.scale == 1.0:
+            return ctx.K.embed(ctx.token_ids, self.table)
+        return ctx.K.embed(ctx.token_ids, self.table, self.scale)
 
 
 class OutputHead(Part):

@@ -60,3 +60,31 @@ class DenseMLP(FeedForward):
     def forward(self, ctx, h, residual):
         K = ctx.K
         K.linear(K.linear_act(h, self.w_up, self.activation, ctx.dtype), self.w_down, add_to=residual)
+
+
+class ClampedGLU(FeedForward):
+    """``down(g * sigmoid(alpha g) * (u + shift))`` with ``g = min(gate(x), limit)`` and ``u = clamp(up(x), -limit, limit)``, no
+    biases. ``gate`` and ``up`` are one matrix ``[2 * intermediate, hidden]`` (gate rows first); the gated unit is computed in
+    32-bit on the product's sums where those are at hand (small batches)."""
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, intermediate: int, gate_name: str, up_name: str, down_name: str, limit: float, alpha: float = 1.702,
+                 shift: float = 1.0):
+        if not limit > 0:
+            raise ValueError(f"the limit of a clamped gated unit must be positive, got {limit}")
+        self.hidden, self.intermediate = hidden, intermediate
+        self.gate_name, self.up_name, self.down_name = gate_name, up_name, down_name
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        self.w_gate_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        h, i = self.hidden, self.intermediate
+        return {"w_gate_up": ParamSpec((Source(self.gate_name, (i, h)), Source(self.up_name, (i, h))), MATRIX),
+                "w_down": ParamSpec((Source(self.down_name, (h, i)),), MATRIX)}
+
+    def forward(self, ctx, h, residual):
+        K = ctx.K
+        y = K.glu_clamped(K.linear(h, self.w_gate_up, transient=True), self.limit, self.alpha, self.shift, ctx.dtype)
+        K.linear(y, self.w_down, add_to=residual)

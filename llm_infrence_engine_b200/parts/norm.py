@@ -1,4 +1,4 @@
-"""RMS normalisation of rows of the 32-bit residual stream."""
+"""Normalisation of rows of the 32-bit residual stream: root mean square, and layer norm with a weight."""
 from __future__ import annotations
 
 from typing import Dict, Optional
@@ -45,3 +45,30 @@ class RMSNorm(Norm):
 
     def norm_rows(self, ctx, residual, rows):
         return ctx.K.rmsnorm_rows(residual, None, self.weight, self.eps, rows, ctx.dtype)
+
+
+class LayerNorm(Norm):
+    """``y = (x - mean) / sqrt(var + eps) * weight`` without a bias, the variance being the mean squared deviation; mean,
+    variance and scaling in 32-bit, one rounding of the result.
+
+    The same norm also closes a sublayer: ``add_normed(ctx, residual, y)`` is ``residual += norm(y)``. That addition is put
+    off until the next norm of the stream, whose kernel adds and normalises in one pass.
+    """
+
+    graph_safe = True
+
+    def __init__(self, dim: int, eps: float, weight_name: str):
+        self.dim, self.eps, self.weight_name = dim, float(eps), weight_name
+        self.weight: Optional[torch.Tensor] = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {"weight": ParamSpec((Source(self.weight_name, (self.dim,), INIT_NORM),), VECTOR)}
+
+    def norm(self, ctx, residual):
+        return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype)
+
+    def norm_rows(self, ctx, residual, rows):
+        return ctx.K.layernorm(residual, self.weight, self.eps, ctx.dtype, rows)
+
+    def add_normed(self, ctx, residual, y) -> None:
+        ctx.K.post_norm_add(residual, y, self.weight, self.eps)

@@ -1,0 +1,187 @@
+"""Mixers that carry a state of fixed size from token to token, and two mixers side by side."""
+from __future__ import annotations
+
+from typing import Dict, Optional, Sequence
+
+import torch
+
+from ..cache.spec import FixedStateSpec
+from .base import (ANY, INIT_LOG_RATE, INIT_NORM, INIT_NORMAL, INIT_PROJ, INIT_SMALL, INIT_STEP_BIAS, INIT_TAPS, MATRIX, VECTOR, Mixer, ParamSpec,
+                   Part, Source)
+
+
+def _padded(w: torch.Tensor, multiple: int = 8) -> torch.Tensor:
+    """Rows added so that every row of the product starts on a 16-byte boundary."""
+    pad = -w.shape[0] % multiple
+    return torch.cat([w, w.new_zeros((pad, w.shape[1]))]).contiguous() if pad else w
+
+
+class GatedDeltaMixer(Mixer):
+    """The gated delta rule with one decay per head AND key channel. With q, k of ``num_kv_heads x head_dim`` and v of
+    ``num_heads x v_head_dim`` (head ``h`` uses q/k head ``h // (num_heads // num_kv_heads)``), each through a short causal
+    convolution and SiLU, q and k then made unit vectors per head (``x / sqrt(sum x^2 + 1e-6)``, q also times ``head_dim^-1/2``):
+
+        beta = sigmoid(W_b x)                                                  one per head
+        g    = exp(-exp(A_log[h]) * softplus(W_a2 (W_a1 x) + dt_bias))         heads x head_dim
+        S <- g (.) S (row d by g[d]);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+
+    per head, ``S [head_dim, v_head_dim]`` starting at zero. Each head's ``o`` is divided by its root mean square, multiplied by
+    a weight shared by the heads and by ``sigmoid(W_g2 (W_g1 x))``; then the output projection. The ranks of the two low-rank
+    projections are read off the checkpoint. Decays, gates, unit norms and the state are 32-bit; a request's state is ``S`` and
+    the convolution's last ``conv_taps - 1`` inputs.
+    """
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, conv_taps: int, eps: float, prefix: str,
+                 random_rank: int = 16):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} query/key heads")
+        if not 2 <= conv_taps <= 8:
+            raise ValueError(f"a short convolution has 2 to 8 taps, got {conv_taps}")
+        if head_dim > 256:
+            raise ValueError(f"the delta rule's kernel keeps a column of the state in registers: head_dim {head_dim} is more than 256")
+        self.hidden, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim = hidden, num_heads, num_kv_heads, head_dim, v_head_dim
+        self.conv_taps, self.eps, self.prefix, self.random_rank = int(conv_taps), float(eps), prefix, random_rank
+        self.qk = num_kv_heads * head_dim
+        self.channels = 2 * self.qk + num_heads * v_head_dim      # what the convolution sees: q | k | v
+        self.b_col = self.channels
+        self.a1_col = self.b_col + num_heads
+        self.w_in = self.w_a2 = self.w_g2 = self.w_o = self.conv_w = self.A_log = self.dt_bias = self.norm_w = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p, h, H, D, DV = self.prefix, self.hidden, self.num_heads, self.head_dim, self.v_head_dim
+        rows = (("q", self.qk), ("k", self.qk), ("v", H * DV))
+        r = self.random_rank
+        return {
+            "w_in": ParamSpec(tuple(Source(f"{p}.{n}", (c, h), INIT_PROJ) for n, c in rows)
+                              + (Source(f"{p}.b", (H, h), INIT_PROJ), Source(f"{p}.a1", (ANY, h), INIT_PROJ, free=r),
+                                 Source(f"{p}.g1", (ANY, h), INIT_PROJ, free=r)), MATRIX),
+            "w_a2": ParamSpec((Source(f"{p}.a2", (H * D, ANY), INIT_PROJ, free=r),), MATRIX),
+            "w_g2": ParamSpec((Source(f"{p}.g2", (H * DV, ANY), INIT_PROJ, free=r),), MATRIX),
+            "w_o": ParamSpec((Source(f"{p}.o", (h, H * DV), INIT_PROJ),), MATRIX),
+            "conv_w": ParamSpec(tuple(Source(f"{p}.{n}.conv", (c, self.conv_taps), INIT_TAPS) for n, c in rows), VECTOR),
+            "A_log": ParamSpec((Source(f"{p}.A_log", (H,), INIT_LOG_RATE),), VECTOR),
+            "dt_bias": ParamSpec((Source(f"{p}.dt_bias", (H * D,), INIT_STEP_BIAS),), VECTOR),
+            "norm_w": ParamSpec((Source(f"{p}.norm", (DV,), INIT_NORM),), VECTOR),
+        }
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        self.rank_a, self.rank_g = self.w_a2.shape[1], self.w_g2.shape[1]
+        if self.w_in.shape[0] != self.a1_col + self.rank_a + self.rank_g:
+            raise ValueError(f"{self.prefix}: the two halves of a low-rank projection do not agree on its rank")
+        self.g1_col = self.a1_col + self.rank_a
+        self.w_in = _padded(self.w_in)
+
+    def cache_spec(self):
+        return (FixedStateSpec((self.num_heads, self.head_dim, self.v_head_dim)), FixedStateSpec((self.conv_taps - 1, self.channels)))
+
+    def forward(self, ctx, h, cache, residual):
+        K = ctx.K
+        state, conv_state = cache
+        H, G, D, DV = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        z = K.linear(h, self.w_in, out_dtype=ctx.dtype)
+        qkv = K.causal_conv(z, 0, self.channels, self.conv_w, None, conv_state.state, ctx, activation="silu")
+        a = K.linear(z[:, self.a1_col:self.a1_col + self.rank_a].contiguous(), self.w_a2, out_dtype=ctx.dtype)
+        g = K.linear(z[:, self.g1_col:self.g1_col + self.rank_g].contiguous(), self.w_g2, out_dtype=ctx.dtype)
+        o = K.delta_rule(qkv, H, G, D, DV, a, z, self.b_col, self.A_log, self.dt_bias, state.state, ctx)
+        y = K.group_rmsnorm_gate(o, g, 0, self.norm_w, DV, self.eps, gate_first=False, out_dtype=ctx.dtype)
+        K.linear(y, self.w_o, add_to=residual)
+
+
+class StateSpaceMixer(Mixer):
+    """A selective state-space mixer with one decay per head (the recurrence of Mamba-2). ``W_in x`` is laid out as
+    ``[z: inner | x: inner | B: groups * state | C: groups * state | dt: heads]`` with ``inner = heads * v_head_dim``; x, B and C
+    together pass a short causal convolution with a bias and SiLU; ``dt <- softplus(dt + dt_bias)`` without a clamp; per head
+    (head ``h`` uses group ``h // (heads // groups)``), ``S [state, v_head_dim]`` starting at zero:
+
+        S <- exp(-exp(A_log[h]) dt) S + dt B x^T;   y = S^T C + D[h] x
+
+    ``y`` is multiplied by ``silu(z)`` and THEN normed by its root mean square in ``norm_groups`` equal parts, times a weight per
+    channel; then the output projection. Step sizes, decays and the state are 32-bit; a request's state is ``S`` and the
+    convolution's last ``conv_taps - 1`` inputs.
+    """
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, num_heads: int, v_head_dim: int, state_size: int, groups: int, norm_groups: int, conv_taps: int,
+                 eps: float, prefix: str):
+        if num_heads % groups:
+            raise ValueError(f"{num_heads} heads cannot share {groups} groups")
+        inner = num_heads * v_head_dim
+        if inner % norm_groups:
+            raise ValueError(f"{inner} channels cannot be normed in {norm_groups} equal parts")
+        if not 2 <= conv_taps <= 8:
+            raise ValueError(f"a short convolution has 2 to 8 taps, got {conv_taps}")
+        if state_size > 256:
+            raise ValueError(f"the recurrence's kernel keeps a column of the state in registers: state size {state_size} is more than 256")
+        self.hidden, self.num_heads, self.v_head_dim, self.state_size, self.groups = hidden, num_heads, v_head_dim, state_size, groups
+        self.norm_groups, self.conv_taps, self.eps, self.prefix = norm_groups, int(conv_taps), float(eps), prefix
+        self.inner = inner
+        self.channels = inner + 2 * groups * state_size            # what the convolution sees: x | B | C
+        self.dt_col = inner + self.channels
+        self.w_in = self.w_o = self.conv_w = self.conv_b = self.dt_bias = self.A_log = self.skip = self.norm_w = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        p, h, H = self.prefix, self.hidden, self.num_heads
+        return {
+            "w_in": ParamSpec((Source(f"{p}.in", (self.dt_col + H, h), INIT_PROJ),), MATRIX),
+            "w_o": ParamSpec((Source(f"{p}.o", (h, self.inner), INIT_PROJ),), MATRIX),
+            "conv_w": ParamSpec((Source(f"{p}.conv", (self.channels, self.conv_taps), INIT_TAPS),), VECTOR),
+            "conv_b": ParamSpec((Source(f"{p}.conv.b", (self.channels,), INIT_SMALL),), VECTOR),
+            "dt_bias": ParamSpec((Source(f"{p}.dt_bias", (H,), INIT_STEP_BIAS),), VECTOR),
+            "A_log": ParamSpec((Source(f"{p}.A_log", (H,), INIT_LOG_RATE),), VECTOR),
+            "skip": ParamSpec((Source(f"{p}.D", (H,), INIT_NORM),), VECTOR),
+            "norm_w": ParamSpec((Source(f"{p}.norm", (self.inner,), INIT_NORM),), VECTOR),
+        }
+
+    def bind(self, tensors) -> None:
+        super().bind(tensors)
+        self.w_in = _padded(self.w_in)
+
+    def cache_spec(self):
+        return (FixedStateSpec((self.num_heads, self.state_size, self.v_head_dim)), FixedStateSpec((self.conv_taps - 1, self.channels)))
+
+    def forward(self, ctx, h, cache, residual):
+        K = ctx.K
+        state, conv_state = cache
+        z = K.linear(h, self.w_in, out_dtype=ctx.dtype)
+        xbc = K.causal_conv(z, self.inner, self.channels, self.conv_w, self.conv_b, conv_state.state, ctx, activation="silu")
+        y = K.ssm_scan(xbc, self.num_heads, self.groups, self.state_size, self.v_head_dim, z, self.dt_col, self.A_log, self.dt_bias, self.skip,
+                       state.state, ctx)
+        y = K.group_rmsnorm_gate(y, z, 0, self.norm_w, self.inner // self.norm_groups, self.eps, gate_first=True, out_dtype=ctx.dtype)
+        K.linear(y, self.w_o, add_to=residual)
+
+
+class ParallelMixer(Mixer):
+    """Two mixers side by side on the same input: the result is half the sum of their outputs, each first divided by its root
+    mean square over the model width and multiplied by a weight of its own. Each keeps its own cache or state."""
+
+    graph_safe = True
+
+    def __init__(self, hidden: int, left: Mixer, right: Mixer, eps: float, left_weight: str, right_weight: str):
+        self.hidden, self.left, self.right, self.eps = hidden, left, right, float(eps)
+        self.left_weight, self.right_weight = left_weight, right_weight
+        self.w_left: Optional[torch.Tensor] = None
+        self.w_right: Optional[torch.Tensor] = None
+
+    def params(self) -> Dict[str, ParamSpec]:
+        return {"w_left": ParamSpec((Source(self.left_weight, (self.hidden,), INIT_NORM),), VECTOR),
+                "w_right": ParamSpec((Source(self.right_weight, (self.hidden,), INIT_NORM),), VECTOR)}
+
+    def children(self) -> Sequence[Part]:
+        return (self.left, self.right)
+
+    def cache_spec(self):
+        return (self.left.cache_spec(), self.right.cache_spec())
+
+    def forward(self, ctx, h, cache, residual):
+        K = ctx.K
+        a = K.zeros_like_rows(residual, 1)
+        self.left.forward(ctx, h, cache[0], a)
+        a = K.take_result(a)
+        b = K.zeros_like_rows(residual, 2)
+        self.right.forward(ctx, h, cache[1], b)
+        b = K.take_result(b)
+        K.dual_rmsnorm_mix(a, b, self.w_left, self.w_right, self.eps, 0.5, add_to=residual)

@@ -8,13 +8,15 @@ Matrices, embeddings and biases are N(0, std); weights of norms are 1 + U(-0.1, 
 from __future__ import annotations
 
 import json
+import math
 from pathlib import Path
 from typing import Any, Dict, Mapping
 
 import torch
 
 from ..models.registry import build_model_spec
-from ..parts.base import INIT_EYE, INIT_NORM, INIT_NORMAL, INIT_ONES, INIT_SHARE, INIT_SMALL
+from ..parts.base import (INIT_EYE, INIT_LOG_RATE, INIT_NORM, INIT_NORMAL, INIT_ONES, INIT_PROJ, INIT_SHARE, INIT_SMALL, INIT_STEP_BIAS,
+                          INIT_TAPS)
 from .safetensors_io import write_safetensors_stream
 
 _STORE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
@@ -46,6 +48,15 @@ def _draw(s, gen: torch.Generator, std: float) -> torch.Tensor:
         return 1.0 + torch.randn(shape, generator=gen) * 0.05
     if s.init == INIT_EYE:
         return torch.eye(shape[-1]) + torch.randn(shape, generator=gen) * 0.05
+    if s.init == INIT_LOG_RATE:
+        return torch.log(0.5 + 3.5 * torch.rand(shape, generator=gen))
+    if s.init == INIT_STEP_BIAS:
+        step = torch.exp(torch.rand(shape, generator=gen) * (math.log(0.3) - math.log(0.01)) + math.log(0.01))
+        return step + torch.log(-torch.expm1(-step))
+    if s.init == INIT_TAPS:
+        return torch.randn(shape, generator=gen) * 0.3
+    if s.init == INIT_PROJ:
+        return torch.randn(shape, generator=gen) / math.sqrt(shape[-1])
     raise ValueError(f"tensor '{s.name}' asks for unknown initialisation '{s.init}'")
 
 

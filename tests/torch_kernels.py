@@ -20,8 +20,8 @@ class TorchKernels:
     def __init__(self):
         self.launches = 0
 
-    def embed(self, token_ids, table):
-        return table[token_ids.long()].float()
+    def embed(self, token_ids, table, scale=1.0):
+        return table[token_ids.long()].float() * scale
 
     def feed_tokens(self, token_ids, source_rows, previous_tokens):
         take = source_rows >= 0
@@ -31,9 +31,9 @@ class TorchKernels:
         fresh = positions[seq_starts[: seq_slots.shape[0]].long()] == 0
         state[seq_slots[fresh].long()] = 0
 
-    def rope_tables(self, positions, inv_freq):
+    def rope_tables(self, positions, inv_freq, mult=1.0):
         ang = positions.float()[:, None] * inv_freq.float()[None, :]
-        return ang.cos(), ang.sin()
+        return ang.cos() * mult, ang.sin() * mult
 
     def add_rmsnorm(self, residual, delta, weight, eps, out_dtype):
         if delta is not None:
@@ -121,8 +121,11 @@ class TorchKernels:
         return (g * torch.sigmoid(g) * u).to(gu.dtype)
 
     # ------------------------------------------------------------------ several residual streams
-    def zeros_like_rows(self, streams):
+    def zeros_like_rows(self, streams, index=0):
         return torch.zeros(streams.shape[0], streams.shape[-1], dtype=torch.float32)
+
+    def take_result(self, y):
+        return y
 
     def streams_expand(self, x, streams):
         return x[:, None, :].repeat(1, streams, 1).contiguous()
@@ -156,7 +159,7 @@ class TorchKernels:
 
     def attention_ext(self, q, q_col, num_heads, num_kv_heads, head_dim, v_head_dim, k_pool, v_pool, block_table, token_seq, positions,
                       page_size, scale, window, max_context, temp=(0.0, 0), rel=None, rel_rows=None, sink=None, gate=None, gate_col=0,
-                      gate_per_head=False, batch=None, num_splits=None):
+                      gate_per_head=False, batch=None, num_splits=None, keep_first=0, chunk=0, softcap=0.0):
         N = q.shape[0]
         rep = num_heads // num_kv_heads
         qs = q[:, q_col:q_col + num_heads * head_dim].float().view(N, num_heads, head_dim)
@@ -164,7 +167,9 @@ class TorchKernels:
         for t in range(N):
             p = int(positions[t])
             lo = 0 if not window else max(0, p - window + 1)
-            keys = torch.arange(lo, p + 1)
+            if chunk:
+                lo = max(lo, p // chunk * chunk)
+            keys = torch.cat([torch.arange(0, min(keep_first, lo)), torch.arange(lo, p + 1)])
             pages = block_table[int(token_seq[t])][(keys // page_size)].long()
             offs = (keys % page_size).long()
             k = k_pool[pages, :, offs].float()                                   # [S, kv heads, head_dim]
@@ -174,6 +179,8 @@ class TorchKernels:
                 factor = scale * (1.0 + temp[0] * math.log((p + 1) // temp[1] + 1))
             for h in range(num_heads):
                 s = (k[:, h // rep] @ qs[t, h]) * factor
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
                 if rel is not None:
                     dist = p - keys
                     row = torch.where(dist < rel_rows.shape[0], rel_rows.long()[dist.clamp(max=rel_rows.shape[0] - 1)], rel.shape[0] - 1)
@@ -191,6 +198,134 @@ class TorchKernels:
             else:
                 out = out * torch.sigmoid(gate[:, gate_col:gate_col + num_heads * v_head_dim].float()).view(N, num_heads, v_head_dim)
         return out.reshape(N, num_heads * v_head_dim).to(q.dtype)
+
+    # ------------------------------------------------------------------ layer norm before and after a sublayer
+    @staticmethod
+    def _ln(x, w, eps):
+        mu = x.mean(-1, keepdim=True)
+        d = x - mu
+        return d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+
+    def layernorm(self, residual, weight, eps, out_dtype, rows=None):
+        x = residual if rows is None else residual[rows.long()]
+        return self._ln(x, weight, eps).to(out_dtype)
+
+    def post_norm_add(self, residual, y, weight, eps):
+        residual += self._ln(y.float(), weight, eps)
+
+    def group_rmsnorm_gate(self, x, gate, gate_col, weight, group_size, eps, gate_first, out_dtype):
+        N, C = x.shape
+        z = gate[:, gate_col:gate_col + C].float()
+        v = x * (z * torch.sigmoid(z)) if gate_first else x
+        v = v.view(N, C // group_size, group_size)
+        v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).reshape(N, C)
+        v = v * (weight.float() if weight.shape[0] == C else weight.float().repeat(C // group_size))
+        if not gate_first:
+            v = v * torch.sigmoid(z)
+        return v.to(out_dtype)
+
+    def dual_rmsnorm_mix(self, a, b, weight_a, weight_b, eps, coef, add_to):
+        a, b = a.float(), b.float()
+        add_to += coef * (a * torch.rsqrt(a.pow(2).mean(-1, keepdim=True) + eps) * weight_a.float()
+                          + b * torch.rsqrt(b.pow(2).mean(-1, keepdim=True) + eps) * weight_b.float())
+
+    def glu_clamped(self, gu, limit, alpha, shift, out_dtype=None):
+        i = gu.shape[1] // 2
+        g, u = gu[:, :i].float().clamp(max=limit), gu[:, i:].float().clamp(-limit, limit)
+        return (g * torch.sigmoid(alpha * g) * (u + shift)).to(out_dtype or gu.dtype)
+
+    def qk_norm_rope_store(self, z, num_heads, num_kv_heads, head_dim, v_head_dim, q_weight, k_weight, eps, cos, sin, rot_dims, interleaved,
+                           slot_mapping, k_pool, v_pool, page_size, write_kv=True):
+        N = z.shape[0]
+        nq, nk = num_heads * head_dim, num_kv_heads * head_dim
+        zf = z.float()
+        q, k = zf[:, :nq].reshape(N, num_heads, head_dim), zf[:, nq:nq + nk].reshape(N, num_kv_heads, head_dim)
+        v = zf[:, nq + nk:nq + nk + num_kv_heads * v_head_dim].reshape(N, num_kv_heads, v_head_dim)
+        if q_weight is not None:
+            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_weight.float()
+            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_weight.float()
+
+        def turn(x):
+            if not rot_dims:
+                return x
+            c, s = cos[:, None, :], sin[:, None, :]
+            out = x.clone()
+            if interleaved:
+                a, b = x[..., 0:rot_dims:2], x[..., 1:rot_dims:2]
+                out[..., 0:rot_dims:2], out[..., 1:rot_dims:2] = a * c - b * s, b * c + a * s
+            else:
+                h = rot_dims // 2
+                a, b = x[..., :h], x[..., h:rot_dims]
+                out[..., :h], out[..., h:rot_dims] = a * c - b * s, b * c + a * s
+            return out
+
+        q, k = turn(q), turn(k)
+        if write_kv:
+            page, off = (slot_mapping // page_size).long(), (slot_mapping % page_size).long()
+            k_pool[page, :, off] = k.to(k_pool.dtype)
+            v_pool[page, :, off] = v.to(v_pool.dtype)
+        return q.reshape(N, nq).to(z.dtype)
+
+    # ------------------------------------------------------------------ mixers with a state of fixed size
+    @staticmethod
+    def _requests(batch):
+        starts = [int(x) for x in batch.seq_starts_dev[: batch.num_seqs + 1]]
+        slots = [int(x) for x in batch.seq_slots[: batch.num_seqs]]
+        return [(slots[r], starts[r], starts[r + 1]) for r in range(batch.num_seqs)]
+
+    def causal_conv(self, z, col, channels, weight, bias, state, batch, activation=None):
+        taps = weight.shape[1]
+        out = torch.zeros(z.shape[0], channels)
+        for slot, s0, s1 in self._requests(batch):
+            u = torch.cat([state[slot], z[s0:s1, col:col + channels].float()])       # the last taps - 1 inputs, then the step's rows
+            y = torch.zeros(s1 - s0, channels)
+            for j in range(taps):
+                y = y + u[j:j + s1 - s0] * weight[:, j].float()
+            if bias is not None:
+                y = y + bias.float()
+            out[s0:s1] = y * torch.sigmoid(y) if activation == "silu" else y
+            state[slot] = u[u.shape[0] - (taps - 1):]
+        return out.to(z.dtype)
+
+    def delta_rule(self, qkv, num_heads, num_kv_heads, head_dim, v_head_dim, a, b, b_col, A_log, dt_bias, state, batch, unit_eps=1e-6):
+        N = qkv.shape[0]
+        H, G, D, DV = num_heads, num_kv_heads, head_dim, v_head_dim
+        x = qkv.float()
+        q, k, v = x[:, :G * D].view(N, G, D), x[:, G * D:2 * G * D].view(N, G, D), x[:, 2 * G * D:2 * G * D + H * DV].view(N, H, DV)
+        q = q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + unit_eps) * D ** -0.5
+        k = k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + unit_eps)
+        beta = torch.sigmoid(b[:, b_col:b_col + H].float())
+        decay = torch.exp(-torch.exp(A_log.float())[None, :, None] * torch.nn.functional.softplus(a.float() + dt_bias.float()).view(N, H, D))
+        out = torch.zeros(N, H, DV)
+        for slot, s0, s1 in self._requests(batch):
+            for h in range(H):
+                g = h // (H // G)
+                S = state[slot, h].clone()
+                for n in range(s0, s1):
+                    S = decay[n, h][:, None] * S
+                    u = beta[n, h] * (v[n, h] - S.T @ k[n, g])
+                    S = S + torch.outer(k[n, g], u)
+                    out[n, h] = S.T @ q[n, g]
+                state[slot, h] = S
+        return out.reshape(N, H * DV)
+
+    def ssm_scan(self, xbc, num_heads, groups, state_size, v_head_dim, dt, dt_col, A_log, dt_bias, skip, state, batch):
+        N = xbc.shape[0]
+        H, G, NS, DV = num_heads, groups, state_size, v_head_dim
+        z = xbc.float()
+        x, B, C = z[:, :H * DV].view(N, H, DV), z[:, H * DV:H * DV + G * NS].view(N, G, NS), z[:, H * DV + G * NS:].view(N, G, NS)
+        step = torch.nn.functional.softplus(dt[:, dt_col:dt_col + H].float() + dt_bias.float())
+        decay = torch.exp(-torch.exp(A_log.float())[None, :] * step)
+        out = torch.zeros(N, H, DV)
+        for slot, s0, s1 in self._requests(batch):
+            for h in range(H):
+                g = h // (H // G)
+                S = state[slot, h].clone()
+                for n in range(s0, s1):
+                    S = decay[n, h] * S + step[n, h] * torch.outer(B[n, g], x[n, h])
+                    out[n, h] = S.T @ C[n, g] + skip[h] * x[n, h]
+                state[slot, h] = S
+        return out.reshape(N, H * DV)
 
     # ------------------------------------------------------------------ latent attention
     @staticmethod
