@@ -559,10 +559,18 @@ def model_points(folder: Path, vocab: int, batch: int, context: int, prefill_tok
     cfg = EngineConfig(dtype="bfloat16", block_size=BLOCK, num_blocks=batch * per_seq + 1, max_seqs=batch, max_len=context + 8,
                        max_num_batched_tokens=max(batch, 16), cuda_graphs=True)
     spec, cache, runner = build_runner(folder, cfg)
+
+    def fill(b):   # synthetic cache contents; states of fixed size keep their zeros
+        if isinstance(b, tuple):
+            for x in b:
+                fill(x)
+        elif hasattr(b, "k"):
+            b.k.normal_(0, 0.5)
+            if b.v is not None:
+                b.v.normal_(0, 0.5)
+
     for b in runner.bindings:
-        b.k.normal_(0, 0.5)
-        if b.v is not None:
-            b.v.normal_(0, 0.5)
+        fill(b)
     entries = []
     for i in range(batch):
         cache.admit(i)
@@ -581,8 +589,22 @@ def model_points(folder: Path, vocab: int, batch: int, context: int, prefill_tok
     torch.cuda.synchronize()
     runner.K.check_device_errors()
     dec_ms = start.elapsed_time(stop) / steps
-    held = sum(min(context, getattr(g, "window", None) or context) * g.num_kv_heads * (g.head_dim + (g.head_dim if g.v_head_dim is None else g.v_head_dim))
-               for g in spec.cache_specs()) * 2
+    from llm_infrence_engine_b200.cache.spec import FixedStateSpec, flatten_specs
+
+    def live(g):   # bytes of one request's cache entry that a decode step reads (a state of fixed size is also written back)
+        if isinstance(g, FixedStateSpec):
+            n = 1
+            for d in g.shape:
+                n *= d
+            return 2 * 4 * n
+        seen = min(context, getattr(g, "window", None) or context)
+        if getattr(g, "chunk", None):
+            seen = min(seen, (context - 1) % g.chunk + 1)
+        if getattr(g, "window", None):
+            seen = min(context, seen + getattr(g, "keep_first", 0))
+        return 2 * seen * g.num_kv_heads * (g.head_dim + (g.head_dim if g.v_head_dim is None else g.v_head_dim))
+
+    held = sum(live(g) for cs in spec.cache_specs() for g in flatten_specs(cs))
     out = {"decode_ms": round(dec_ms, 4), "decode_tok_s": round(batch / dec_ms * 1e3, 1), "launches_per_step": cap.launches,
            "decode_bytes": runner.weight_bytes_per_step() + batch * held}
     del runner, spec, cache, cap
@@ -723,6 +745,175 @@ def luvutar_kernel_points(torch, pk) -> dict:
     return out
 
 
+# ``--workload zepalorn``: the Zepalorn decoder at layer sizes of real models, beside the Qwen2 decoder of equal size.
+
+ZEPALORN_SIZES = {
+    # name: (width, attention heads, kv heads, head_dim, window, chunk, delta heads, delta key size, delta value size, state-space heads,
+    #        state-space value size, state size, state groups, ff, layers, vocab)
+    "0.5b-like": (896, 14, 2, 64, 1024, 2048, 8, 64, 128, 28, 64, 128, 2, 2432, 8, 32768),
+    "3b-like": (2048, 16, 4, 128, 2048, 4096, 16, 128, 128, 64, 64, 128, 8, 5504, 8, 32768),
+}
+
+
+def zepalorn_config(size: str) -> dict:
+    """Layers in the order delta rule, windowed attention, attention beside a state-space mixer, delta rule, ..."""
+    W, H, G, d, win, chunk, dh, dd, dv, sh, sv, ns, sg, ff, layers, vocab = ZEPALORN_SIZES[size]
+    scaling = {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}
+    kinds = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+        if i % 4 in (0, 3):
+            kinds.append({"type": "channel_delta", "mixer": {"heads": dh, "kv_heads": dh, "dim": dd, "vdim": dv, "conv": 4}, "mlp": mlp})
+        elif i % 4 == 1:
+            m = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "mask": {"size": win, "keep_first": 4},
+                 "rot": {"base": 1000000.0, "dims": d, "scaling": scaling}}
+            kinds.append({"type": "attention", "mixer": m, "mlp": mlp})
+        else:
+            left = {"heads": H, "kv_heads": G, "dim": d, "vdim": d, "scale": d ** -0.5, "conv": 4, "softcap": 50.0, "mask": {"size": chunk},
+                    "rot": {"base": 10000.0, "dims": d // 2, "scaling": scaling}}
+            right = {"heads": sh, "vdim": sv, "state": ns, "groups": sg, "norm_groups": sg, "conv": 4}
+            kinds.append({"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp})
+    return {"architecture": "Zepalorn", "vocab": vocab, "width": W, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": kinds}
+
+
+def qwen2_beside_zepalorn(size: str) -> dict:
+    W, H, G, d, win, chunk, dh, dd, dv, sh, sv, ns, sg, ff, layers, vocab = ZEPALORN_SIZES[size]
+    return {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "vocab_size": vocab, "hidden_size": W, "head_dim": d,
+            "intermediate_size": ff, "num_hidden_layers": layers, "num_attention_heads": H, "num_key_value_heads": G, "rms_norm_eps": 1e-6,
+            "rope_theta": 10000.0, "tie_word_embeddings": True, "max_position_embeddings": 32768, "use_sliding_window": False, "hidden_act": "silu"}
+
+
+def zepalorn_kernel_points(torch, pk) -> dict:
+    """Zepalorn's kernels one by one at the 3b-like layer sizes, each beside the Qwen2 kernel that does the like job at the same
+    size where there is one: microseconds, and the fraction of its roofline (bytes that must move / copy peak, or flops / bf16
+    peak). The recurrences have no tensor-core form here: their flops are set against the bf16 peak all the same, and their bytes
+    (state in and out for decoded tokens; projections in, results out for a prompt) against the copy peak."""
+    from types import SimpleNamespace
+
+    from llm_infrence_engine_b200.csrc import get_kernels
+
+    K = get_kernels()
+    W, H, G, d, win, chunk, dh, dd, dv, sh, sv, ns, sg, ff, _, _ = ZEPALORN_SIZES["3b-like"]
+    bf, dev = torch.bfloat16, "cuda"
+    hbm, tf = pk["hbm_gbs"] * 1e9, pk["bf16_tflops"] * 1e12
+    out = {}
+
+    def entry(us, bytes_=None, flops=None):
+        e = {"us": round(us, 2)}
+        if bytes_ is not None:
+            e["frac_of_copy_peak"] = round(bytes_ / (us * 1e-6) / hbm, 4)
+        if flops is not None:
+            e["frac_of_bf16_peak"] = round(flops / (us * 1e-6) / tf, 4)
+        return e
+
+    def batch_of(lens, slots=None):
+        starts = [0]
+        for n in lens:
+            starts.append(starts[-1] + n)
+        return SimpleNamespace(seq_lens=list(lens), seq_starts_dev=torch.tensor(starts, dtype=torch.int32, device=dev), num_seqs=len(lens),
+                               seq_slots=torch.tensor(slots or list(range(len(lens))), dtype=torch.int32, device=dev), max_seq_len=max(lens), _tables={})
+
+    def tables(batch, ctx, page=BLOCK):
+        per = -(-ctx // page)
+        t = torch.zeros((batch + 1, per), dtype=torch.int32, device=dev)
+        t[:batch] = (torch.randperm(batch * per, device=dev).to(torch.int32) + 1).view(batch, per)
+        return t, batch * per + 1
+
+    for what, batch, ctx, T in (("decode", 8, 4096, 1), ("decode_b64", 64, 4096, 1), ("prefill", 1, 2048, 2048)):
+        table, pages = tables(batch, ctx)
+        N = batch * T
+        seq = torch.arange(batch, dtype=torch.int32, device=dev).repeat_interleave(T)
+        pos = (torch.arange(T, dtype=torch.int32, device=dev) + (ctx - T)).repeat(batch)
+        b = batch_of([T] * batch)
+        kp = torch.randn(pages, G, BLOCK, d, device=dev).to(bf)
+        vp = torch.randn(pages, G, BLOCK, d, device=dev).to(bf)
+        qkv = torch.randn(N, (H + 2 * G) * d, device=dev).to(bf)
+        if T == 1:
+            moved, fl = batch * ctx * 2 * G * d * 2, None
+            moved_w, fl_w = batch * (win + 4) * 2 * G * d * 2, None
+        else:
+            moved, fl = None, 4.0 * H * d * (T * (T + 1) / 2) * batch
+            moved_w, fl_w = None, 4.0 * H * d * sum(min(p + 1, win + 4) for p in range(ctx - T, ctx)) * batch
+        out[f"attention_{what}_qwen2"] = entry(_time(lambda: (b._tables.clear(), K.paged_attention(qkv, kp, vp, table, seq, pos, H, G, d, BLOCK, d ** -0.5, 0, ctx, batch=b)), torch), moved, fl)
+        out[f"attention_{what}_qwen2_window"] = entry(_time(lambda: (b._tables.clear(), K.paged_attention(qkv, kp, vp, table, seq, pos, H, G, d, BLOCK, d ** -0.5, win, ctx, batch=b)), torch), moved_w, fl_w)
+        out[f"attention_{what}_zepalorn_window_kept"] = entry(_time(lambda: (b._tables.clear(), K.attention_ext(qkv, 0, H, G, d, d, kp, vp, table, seq, pos, BLOCK, d ** -0.5, win, ctx, batch=b, keep_first=4)), torch), moved_w, fl_w)
+        out[f"attention_{what}_zepalorn_chunk_cap"] = entry(_time(lambda: (b._tables.clear(), K.attention_ext(qkv, 0, H, G, d, d, kp, vp, table, seq, pos, BLOCK, d ** -0.5, 0, ctx, batch=b, chunk=chunk, softcap=50.0)), torch), moved, fl)
+        del kp, vp
+        # the recurrences: state in and out for every request; for a prompt, the projections in and the result out
+        qk = torch.randn(N, 2 * dh * dd + dh * dv, device=dev).to(bf) * 0.5
+        a_, b_ = torch.randn(N, dh * dd, device=dev).to(bf), torch.randn(N, dh, device=dev).to(bf)
+        A_log, dt_bias = torch.zeros(dh, device=dev), torch.full((dh * dd,), -3.0, device=dev)
+        state = torch.zeros(batch + 1, dh, dd, dv, device=dev)
+        moved = batch * 2 * 4 * dh * dd * dv + N * (2 * (3 * dh * dd + dh * dv) + 4 * dh * dv)
+        out[f"delta_rule_{what}_zepalorn"] = entry(_time(lambda: K.delta_rule(qk, dh, dh, dd, dv, a_, b_, 0, A_log, dt_bias, state, b), torch), moved, 8.0 * N * dh * dd * dv)
+        xbc = torch.randn(N, sh * sv + 2 * sg * ns, device=dev).to(bf) * 0.5
+        dt = torch.randn(N, sh, device=dev).to(bf)
+        A2, bias2, skip = torch.zeros(sh, device=dev), torch.full((sh,), -3.0, device=dev), torch.ones(sh, device=dev)
+        state2 = torch.zeros(batch + 1, sh, ns, sv, device=dev)
+        moved = batch * 2 * 4 * sh * ns * sv + N * (2 * (sh * sv + 2 * sg * ns) + 4 * sh * sv)
+        out[f"state_space_{what}_zepalorn"] = entry(_time(lambda: K.ssm_scan(xbc, sh, sg, ns, sv, dt, 0, A2, bias2, skip, state2, b), torch), moved, 6.0 * N * sh * ns * sv)
+        C = 2 * dh * dd + dh * dv
+        cw, cs = torch.randn(C, 4, device=dev), torch.zeros(batch + 1, 3, C, device=dev)
+        out[f"convolution_{what}_zepalorn"] = entry(_time(lambda: K.causal_conv(qk, 0, C, cw, None, cs, b, "silu"), torch), N * C * 4 + batch * C * 3 * 8)
+    # norms at 2,048 rows: add + norm of the stream against norm of the result + add + norm of the stream
+    N = 2048
+    res, delta, w = torch.randn(N, W, device=dev), torch.randn(N, W, device=dev).to(bf), torch.ones(W, device=dev)
+    out["norm_qwen2"] = entry(_time(lambda: K.add_rmsnorm(res, delta, w, 1e-6, bf), torch), N * W * (4 + 4 + 2 + 2))
+
+    def both():
+        K.post_norm_add(res, delta, w, 1e-6)
+        return K.layernorm(res, w, 1e-6, bf)
+
+    out["norm_zepalorn"] = entry(_time(both, torch), N * W * (4 + 4 + 2 + 2))
+    # feed-forward going in: the tcgen05 product with SiLU in its epilogue against the library product + the clamped gated unit
+    h = torch.randn(N, W, device=dev).to(bf)
+    wgu = torch.randn(2 * ff, W, device=dev).to(bf) * 0.02
+    out["ff_in_qwen2"] = entry(_time(lambda: K.gate_up_act(h, wgu, bf), torch), None, 2.0 * N * W * 2 * ff)
+    out["ff_in_zepalorn"] = entry(_time(lambda: K.glu_clamped(K.linear(h, wgu, transient=True), 7.0, 1.702, 1.0, bf), torch), None, 2.0 * N * W * 2 * ff)
+    # gated norms of the recurrences' results and the mean of the two halves of a side-by-side mixer (no counterpart in Qwen2)
+    o, g = torch.randn(N, dh * dv, device=dev), torch.randn(N, dh * dv, device=dev).to(bf)
+    nw = torch.ones(dv, device=dev)
+    out["gated_norm_zepalorn"] = entry(_time(lambda: K.group_rmsnorm_gate(o, g, 0, nw, dv, 1e-6, False, bf), torch), N * dh * dv * (4 + 2 + 2))
+    a2, b2, y = torch.randn(N, W, device=dev).to(bf), torch.randn(N, W, device=dev).to(bf), torch.zeros(N, W, device=dev)
+    out["mean_of_two_zepalorn"] = entry(_time(lambda: K.dual_rmsnorm_mix(a2, b2, w, w, 1e-6, 0.5, y), torch), N * W * (2 + 2 + 4 + 4))
+    K.check_device_errors()
+    return out
+
+
+def zepalorn_workload(a) -> int:
+    import torch
+
+    from llm_infrence_engine_b200.weights import write_random_model
+
+    pk = peaks()
+    sampler = ClockSampler()
+    sampler.start()
+    sizes = {}
+    steps = min(a.steps, 256)
+    for size in ZEPALORN_SIZES:
+        vocab = ZEPALORN_SIZES[size][-1]
+        row = {}
+        for name, config in (("zepalorn", zepalorn_config(size)), ("qwen2", qwen2_beside_zepalorn(size))):
+            with tempfile.TemporaryDirectory() as tmp:
+                folder = write_random_model(config, Path(tmp) / "model", seed=0, store_dtype="bfloat16")
+                pt = model_points(folder, vocab, a.batch, a.context or 4096, a.prefill_tokens, steps, max(a.warmup, 3), torch)
+            pt["decode_frac_of_copy_peak"] = round(pt["decode_bytes"] / (pt["decode_ms"] * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            row[name] = pt
+        sizes[size] = row
+    names = ("width", "heads", "kv_heads", "head_dim", "window", "chunk", "delta_heads", "delta_dim", "delta_vdim", "ssm_heads", "ssm_vdim", "ssm_state",
+             "ssm_groups", "ff", "layers", "vocab")
+    line = {"metric": f"Zepalorn beside Qwen2 of equal size: decode (batch {a.batch}, context {a.context or 4096}) and prefill ({a.prefill_tokens} tokens), bf16, random weights",
+            "unit": "ms and tokens/s per size", "n_gpus": 1, "impl": "ours", "dtype": "bf16", "steps": steps, "warmup": max(a.warmup, 3),
+            "data": "synthetic: random weights (seed 0), uniform random token ids, synthetic cache contents",
+            "config": {"sizes": {k: dict(zip(names, v)) for k, v in ZEPALORN_SIZES.items()}, "block_size": BLOCK, "peaks": pk["source"],
+                       "l2": "weights + cache per step larger than L2, no flush"},
+            "clocks": sampler.stop(), "sizes": sizes}
+    if a.kernels:
+        line["kernels"] = zepalorn_kernel_points(torch, pk)
+    print(json.dumps(line))
+    return 0
+
+
 def luvutar_workload(a) -> int:
     import torch
 
@@ -770,7 +961,7 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel of a decode step from the host instead of replaying a CUDA graph")
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="measure one part only (for profiling); the JSON line then lacks the rest")
-    ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar"],
+    ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar", "zepalorn"],
                     help="serving: continuous batching of --requests requests (prompts U[128,2048], outputs U[64,512]) through Engine; "
                          "luvutar: the Luvutar decoder at two layer sizes beside the Qwen2 decoder of equal size (decode and prefill)")
     ap.add_argument("--kernels", action="store_true", help="luvutar: also time its kernels one by one beside their Qwen2 counterparts")
@@ -785,6 +976,8 @@ def main() -> int:
         return 2
     if a.workload == "luvutar":
         return luvutar_workload(a)
+    if a.workload == "zepalorn":
+        return zepalorn_workload(a)
     PREFILL_TOKENS = a.prefill_tokens
     shape_name, changes, shape_context = SHAPES[a.shape]
     MODEL.update(changes)

@@ -76,7 +76,10 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
     pdl_wait();
     int n0 = P.tile_info[2 * blockIdx.x], ntok = min(P.tile_info[2 * blockIdx.x + 1], tokens_per_tile);
     const int p_first = P.positions[n0], p_last = P.positions[n0 + ntok - 1];
-    const int lo = P.window > 0 ? max(0, p_first - P.window + 1) : 0;
+    int lo = P.window > 0 ? max(0, p_first - P.window + 1) : 0;
+    if (P.ex.chunk > 0) lo = max(lo, (p_first / P.ex.chunk) * P.ex.chunk);
+    const int kept = min(P.ex.keep_first, lo);                               // keys [0, kept) are seen besides [lo, hi)
+    const int npre = (split == 0 && kept > 0) ? (kept + KEYS - 1) / KEYS : 0;   // their chunks come first, in the first slice
     const int hi = p_last + 1;
     int per = (hi - lo + P.num_splits - 1) / P.num_splits;
     per = (per + KEYS - 1) / KEYS * KEYS;
@@ -84,7 +87,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
     const int end = min(hi, start + per);
     const int* table = P.block_table + (size_t)P.token_seq[n0] * P.max_blocks;
 
-    int row_pos[2], row_head[2], row_tok[2], row_g[2];
+    int row_pos[2], row_head[2], row_tok[2], row_g[2], row_lo[2];   // row_lo: the first key the row sees apart from the kept ones
     float row_factor[2];
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -95,17 +98,18 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
         row_head[i] = ok ? kvh * G + g : 0;
         row_g[i] = ok ? row % gh : 0;
         row_pos[i] = ok ? P.positions[n0 + t] : -1;
+        row_lo[i] = ok ? attn_ext::first_visible(row_pos[i], P.window, P.ex) : 0;
         float f = P.scale;
         if (P.ex.temp_every > 0 && ok) f = P.scale * (1.0f + P.ex.temp_coef * logf((float)((row_pos[i] + 1) / P.ex.temp_every + 1)));
         row_factor[i] = f;
     }
     const bool warp_live = warp * 16 < ntok * gh;   // a warp without rows only fetches
     // the span of my warp's positions: a chunk that all its rows see in full needs no mask arithmetic
-    int w_min = row_pos[0] < 0 || row_pos[1] < 0 ? -1 : min(row_pos[0], row_pos[1]), w_max = max(row_pos[0], row_pos[1]);
+    int w_min = row_pos[0] < 0 || row_pos[1] < 0 ? -1 : min(row_pos[0], row_pos[1]), w_lo = max(row_lo[0], row_lo[1]);
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         w_min = min(w_min, __shfl_xor_sync(0xffffffffu, w_min, o));   // -1 if any row of the warp is not a row of the tile
-        w_max = max(w_max, __shfl_xor_sync(0xffffffffu, w_max, o));
+        w_lo = max(w_lo, __shfl_xor_sync(0xffffffffu, w_lo, o));      // from this key on, every row of the warp sees what is causal
     }
 
     constexpr int segs = dk / 8, vsegs = dv / 8;
@@ -120,9 +124,9 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
 
     // two threads to a key: one look at the block table per thread and chunk, then every second 16-byte piece of the row
     const int my_key = tid >> 1, odd = tid & 1;
-    auto load_chunk = [&](int base, int stage) {
-        const int key = base + my_key;
-        const bool ok = key < end && key >= lo;
+    auto load_chunk = [&](int c, int stage) {
+        const int key = (c < npre ? c * KEYS : start + (c - npre) * KEYS) + my_key;
+        const bool ok = c < npre ? key < kept : (key < end && key >= lo);
         size_t row = 0;
         if (ok) row = ((size_t)table[key / P.page_size] * P.nkv + kvh) * P.page_size + key % P.page_size;
         const int bytes = ok ? 16 : 0;
@@ -136,8 +140,8 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
         for (int sgm = odd; sgm < vsegs; sgm += 2) cp_async16(vd + sgm * 8, vsrc + sgm * 8, bytes);
     };
 
-    const int nchunks = end > start ? (end - start + KEYS - 1) / KEYS : 0;
-    if (nchunks > 0) load_chunk(start, 0);
+    const int nchunks = npre + (end > start ? (end - start + KEYS - 1) / KEYS : 0);
+    if (nchunks > 0) load_chunk(0, 0);
     cp_commit();
     __syncthreads();
     // my 16 rows of Q as A operands, kept for the whole tile
@@ -152,9 +156,10 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
 
     for (int c = 0; c < nchunks; ++c) {
         const int stage = c & 1;
-        const int base = start + c * KEYS;
+        const int base = c < npre ? c * KEYS : start + (c - npre) * KEYS;
+        const int range_lo = c < npre ? 0 : lo, range_hi = c < npre ? kept : end;
         __syncthreads();                      // everyone is done with the stage that is filled next
-        if (c + 1 < nchunks) load_chunk(base + KEYS, stage ^ 1);
+        if (c + 1 < nchunks) load_chunk(c + 1, stage ^ 1);
         cp_commit();
         cp_wait<1>();
         __syncthreads();                      // chunk c is in shared memory
@@ -179,8 +184,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
         }
         // scale, bias, mask; element (tile t, e): row gid + 8 * (e >> 1), key base + t * 8 + 2 * tig + (e & 1)
         float mx[2] = {-INFINITY, -INFINITY};
-        const bool interior = w_min >= 0 && base + KEYS - 1 <= w_min && base + KEYS <= end && base >= lo &&
-                              (P.window <= 0 || w_max - base < P.window);
+        const bool interior = c >= npre && w_min >= 0 && base + KEYS - 1 <= w_min && base + KEYS <= end && base >= lo && base >= w_lo;
         if (interior) {
 #pragma unroll
             for (int t = 0; t < 8; ++t)
@@ -188,6 +192,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
                 for (int e = 0; e < 4; ++e) {
                     const int i = e >> 1;
                     float v = s[t][e] * row_factor[i];
+                    if (P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
                     if (P.ex.rel) {
                         const int dist = row_pos[i] - (base + t * 8 + 2 * tig + (e & 1));
                         if (P.bias_in_smem) {
@@ -209,10 +214,11 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
                     const int i = e >> 1;
                     const int key = base + t * 8 + 2 * tig + (e & 1);
                     const int p = row_pos[i];
-                    const bool seen = key <= p && key < end && key >= lo && (P.window <= 0 || p - key < P.window);
+                    const bool seen = key <= p && key < range_hi && key >= range_lo && (key >= row_lo[i] || key < P.ex.keep_first);
                     float v = -INFINITY;
                     if (seen) {
                         v = s[t][e] * row_factor[i];
+                        if (P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
                         if (P.ex.rel) {
                             const int dist = p - key;
                             if (P.bias_in_smem) {
@@ -341,7 +347,7 @@ LLMIE_API int llmie_paged_attention_ext_fa(const bf16* q, int q_stride, const bf
                                            bf16* out, float* scratch, int N, int nq, int nkv, int dk, int dv, int page_size, float scale,
                                            int window, int num_splits, float temp_coef, int temp_every, const float* rel, const int* rows_of,
                                            int n_rows_of, int rel_rows, const float* sink, const bf16* gate, int gate_stride, int gate_mode,
-                                           cudaStream_t s) {
+                                           int keep_first, int chunk, float softcap, cudaStream_t s) {
     if (N <= 0 || tiles <= 0) return 0;
     if (nkv <= 0 || nq % nkv || !llmie_attention_ext_fa_fits(dk, dv, v_pool != nullptr, nq / nkv) || !tile_info || page_size <= 0 ||
         num_splits < 1 || (num_splits > 1 && !scratch) || q_stride % 8 || ((uintptr_t)q % 16) || ((uintptr_t)k_pool % 16) ||
@@ -357,6 +363,7 @@ LLMIE_API int llmie_paged_attention_ext_fa(const bf16* q, int q_stride, const bf
     P.head_chunks = (G + P.gh - 1) / P.gh;
     P.ex.temp_coef = temp_coef; P.ex.temp_every = temp_every; P.ex.rel = rel; P.ex.rows_of = rows_of; P.ex.n_rows_of = n_rows_of;
     P.ex.rel_rows = rel_rows; P.ex.sink = sink; P.ex.gate = gate; P.ex.gate_stride = gate_stride; P.ex.gate_mode = gate_mode;
+    P.ex.keep_first = keep_first; P.ex.chunk = chunk; P.ex.softcap = softcap;
     if ((long long)nkv * P.head_chunks > 65535 || num_splits > 65535) return LLMIE_ERR_BAD_ARGUMENT;
     size_t smem = smem_bytes(dk, dv);
     P.bias_in_smem = 0;

@@ -94,7 +94,10 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     else { n0 = blockIdx.x; ntok = 1; }
     ntok = min(ntok, tokens_per_tile);
     const int p_first = P.positions[n0], p_last = P.positions[n0 + ntok - 1];
-    const int lo = P.window > 0 ? max(0, p_first - P.window + 1) : 0;
+    int lo = P.window > 0 ? max(0, p_first - P.window + 1) : 0;
+    if (P.ex.chunk > 0) lo = max(lo, (p_first / P.ex.chunk) * P.ex.chunk);
+    const int kept = min(P.ex.keep_first, lo);                               // keys [0, kept) are seen besides [lo, hi)
+    const int npre = (split == 0 && kept > 0) ? (kept + KEYS - 1) / KEYS : 0;   // their chunks come first, in the first slice
     const int hi = p_last + 1;
     int per = (hi - lo + P.num_splits - 1) / P.num_splits;
     per = (per + KEYS - 1) / KEYS * KEYS;
@@ -103,7 +106,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     const int* table = P.block_table + (size_t)P.token_seq[n0] * P.max_blocks;
 
     // my rows (gid and gid + 8 of each of my row blocks): token, head, position
-    int row_pos[R][2], row_head[R][2], row_tok[R][2], row_g[R][2];
+    int row_pos[R][2], row_head[R][2], row_tok[R][2], row_g[R][2], row_lo[R][2];   // row_lo: the first key the row sees apart from the kept ones
     float row_factor[R][2];
 #pragma unroll
     for (int r = 0; r < R; ++r)
@@ -116,6 +119,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
             row_head[r][i] = ok ? kvh * G + g : 0;
             row_g[r][i] = ok ? row % gh : 0;
             row_pos[r][i] = ok ? P.positions[n0 + t] : -1;
+            row_lo[r][i] = ok ? attn_ext::first_visible(row_pos[r][i], P.window, P.ex) : 0;
             float f = P.scale;
             if (P.ex.temp_every > 0 && ok) f = P.scale * (1.0f + P.ex.temp_coef * logf((float)((row_pos[r][i] + 1) / P.ex.temp_every + 1)));
             row_factor[r][i] = f;
@@ -136,9 +140,9 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     // thread's share of the row's 16-byte pieces (pieces quarter, quarter + 4, ...). Keys outside the slice are filled with zeros.
     const int vsegs = dv >> 3;
     const int my_key = tid >> 2, quarter = tid & 3;
-    auto load_chunk = [&](int base, int stage) {
-        const int key = base + my_key;
-        const bool ok = key < end && key >= lo;
+    auto load_chunk = [&](int c, int stage) {
+        const int key = (c < npre ? c * KEYS : start + (c - npre) * KEYS) + my_key;
+        const bool ok = c < npre ? key < kept : (key < end && key >= lo);
         size_t row = 0;
         if (ok) row = ((size_t)table[key / P.page_size] * P.nkv + kvh) * P.page_size + key % P.page_size;
         const int bytes = ok ? 16 : 0;
@@ -173,18 +177,19 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     // A ring of ST stages: the chunks c + 1 .. c + ST - 1 are on their way while chunk c is worked on (ST = 2 for prompt
     // portions, whose keys come from L2; more for decoded tokens, whose keys come from memory). One group of copies per chunk,
     // also an empty one, so that the count of groups in flight says which chunk has landed.
-    const int nchunks = end > start ? (end - start + KEYS - 1) / KEYS : 0;
+    const int nchunks = npre + (end > start ? (end - start + KEYS - 1) / KEYS : 0);
 #pragma unroll
     for (int i = 0; i < ST - 1; ++i) {
-        if (i < nchunks) load_chunk(start + i * KEYS, i);
+        if (i < nchunks) load_chunk(i, i);
         cp_commit();
     }
 
     for (int c = 0; c < nchunks; ++c) {
         const int stage = c % ST;
-        const int base = start + c * KEYS;
+        const int base = c < npre ? c * KEYS : start + (c - npre) * KEYS;
+        const int range_lo = c < npre ? 0 : lo, range_hi = c < npre ? kept : end;
         __syncthreads();                      // everyone is done with the stage that is filled next, with P and with the sums
-        if (c + ST - 1 < nchunks) load_chunk(base + (ST - 1) * KEYS, (c + ST - 1) % ST);
+        if (c + ST - 1 < nchunks) load_chunk(c + ST - 1, (c + ST - 1) % ST);
         cp_commit();
         cp_wait<ST - 1>();
         __syncthreads();                      // chunk c (and, the first time, the queries) are in shared memory
@@ -244,10 +249,11 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
                     const int i = e >> 1;
                     const int key = base + part * 16 + t * 8 + 2 * tig + (e & 1);
                     const int p = row_pos[r][i];
-                    const bool seen = key <= p && key < end && key >= lo && (P.window <= 0 || p - key < P.window);
+                    const bool seen = key <= p && key < range_hi && key >= range_lo && (key >= row_lo[r][i] || key < P.ex.keep_first);
                     float v = -INFINITY;
                     if (seen) {
                         v = (s[r][t][e] + s2[r][t][e]) * row_factor[r][i];
+                        if (P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
                         if (P.ex.rel) {
                             const int dist = p - key;
                             if (P.bias_in_smem) {
@@ -447,7 +453,7 @@ LLMIE_API int llmie_paged_attention_ext_mma(const bf16* q, int q_stride, const b
                                             int tile_rows, bf16* out, float* scratch, int N, int nq, int nkv, int dk, int dv, int page_size,
                                             float scale, int window, int num_splits, float temp_coef, int temp_every, const float* rel,
                                             const int* rows_of, int n_rows_of, int rel_rows, const float* sink, const bf16* gate,
-                                            int gate_stride, int gate_mode, cudaStream_t s) {
+                                            int gate_stride, int gate_mode, int keep_first, int chunk, float softcap, cudaStream_t s) {
     if (N <= 0 || tiles <= 0) return 0;
     const int fits = llmie_attention_ext_mma_fits(dk, dv, v_pool != nullptr);
     if (nkv <= 0 || nq % nkv || !fits || tile_rows > fits || (tile_rows != 32 && tile_rows != 64 && tile_rows != 128) || page_size <= 0 ||
@@ -464,6 +470,7 @@ LLMIE_API int llmie_paged_attention_ext_mma(const bf16* q, int q_stride, const b
     P.head_chunks = (G + P.gh - 1) / P.gh;
     P.ex.temp_coef = temp_coef; P.ex.temp_every = temp_every; P.ex.rel = rel; P.ex.rows_of = rows_of; P.ex.n_rows_of = n_rows_of;
     P.ex.rel_rows = rel_rows; P.ex.sink = sink; P.ex.gate = gate; P.ex.gate_stride = gate_stride; P.ex.gate_mode = gate_mode;
+    P.ex.keep_first = keep_first; P.ex.chunk = chunk; P.ex.softcap = softcap;
     if ((long long)nkv * P.head_chunks > 65535 || num_splits > 65535) return LLMIE_ERR_BAD_ARGUMENT;
     const dim3 grid(tiles, nkv * P.head_chunks, num_splits);
     const int R = tile_rows / ROWS;

@@ -68,7 +68,7 @@ class CudaKernels:
         # more rows); measured slower at 2,048 tokens (heads of 128: 311 -> 415 us): their registers leave one block per
         # multiprocessor where tiles of 32 rows leave two, and the kernel waits on its barriers, not on the keys
         self.attention_ext_tile_rows = 32
-        self.masked_attention_tensor_cores = False   # kept first tokens, chunks and soft caps on the tensor-core kernels too
+        self.masked_attention_tensor_cores = True    # kept first tokens, chunks and soft caps on the tensor-core kernels too
         self.use_fa_attention_ext = True     # prompt portions with heads of 64 / 128: the kernel in which a warp owns 16 rows and all keys of a chunk
         self.head_matmul_library_rows = 64   # per-head products of latent attention: from this many rows on, one batched library product
         self.slice_keys = 1024         # generic attention: keys per slice, at fixed places of a request (a multiple of 32)
@@ -931,7 +931,7 @@ class CudaKernels:
             group = num_heads // num_kv_heads
             tiles, tile_info = self._tiles(batch, 64 // min(group, 64), q.device)
             blocks = tiles * num_kv_heads * -(-group // 64)
-            span = min(max_context, window) if window else max_context
+            span = min(max_context, window, chunk or max_context) if window else min(max_context, chunk or max_context)
             splits = num_splits or max(1, min((2 * self.num_sms) // max(blocks, 1), -(-span // 64) // 2, 32))
             scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
             self._check(self.lib.llmie_paged_attention_ext_fa(
@@ -940,7 +940,7 @@ class CudaKernels:
                 v_head_dim, page_size, ctypes.c_float(scale), int(window), splits, ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel),
                 _ptr(rel_rows), 0 if rel_rows is None else rel_rows.shape[0], 0 if rel is None else rel.shape[0], _ptr(sink),
                 ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1], gate_mode,
-                self._stream()), "attention_ext (tensor cores, a warp to a row block)")
+                int(keep_first), int(chunk), ctypes.c_float(softcap), self._stream()), "attention_ext (tensor cores, a warp to a row block)")
             if splits > 1:
                 self.launches += 1
             return out
@@ -960,7 +960,7 @@ class CudaKernels:
             else:
                 tiles, tile_info = self._tiles(batch, tile_rows // heads_per_tile, q.device)
             blocks = tiles * num_kv_heads * -(-group // heads_per_tile)
-            span = min(max_context, window) if window else max_context
+            span = min(max_context, window, chunk or max_context) if window else min(max_context, chunk or max_context)
             splits = num_splits or max(1, min((2 * self.num_sms) // max(blocks, 1), -(-span // 64) // 2, 32))
             scratch = self._scratch(N * num_heads * splits * (v_head_dim + 2), q.device) if splits > 1 else None
             self._check(self.lib.llmie_paged_attention_ext_mma(
@@ -969,7 +969,7 @@ class CudaKernels:
                 head_dim, v_head_dim, page_size, ctypes.c_float(scale), int(window), splits, ctypes.c_float(temp[0]), int(temp[1]), _ptr(rel),
                 _ptr(rel_rows), 0 if rel_rows is None else rel_rows.shape[0], 0 if rel is None else rel.shape[0], _ptr(sink),
                 ctypes.c_void_p(0 if gate is None else gate.data_ptr() + gate_col * esize), 0 if gate is None else gate.shape[1], gate_mode,
-                self._stream()), "attention_ext (tensor cores)")
+                int(keep_first), int(chunk), ctypes.c_float(softcap), self._stream()), "attention_ext (tensor cores)")
             if splits > 1:
                 self.launches += 1
             return out
@@ -1036,11 +1036,11 @@ class CudaKernels:
         if (self._pending_post is not None and self._pending_post[0] is residual and self._pending_post[3] == eps
                 and self._pending_add is None and self._pending_streams is None):
             _, y, w_post, _ = self._pending_post
-            self._pending_post = None
-            if rows is not None and y.dtype == torch.bfloat16 and out_dtype == torch.float32:
-                self._pending_post = (residual, y, w_post, eps)
+            if y.dtype == torch.bfloat16 and out_dtype == torch.float32:   # no kernel for this pair: the addition on its own, then the norm
                 y = w_post = None
                 self.flush()
+            else:
+                self._pending_post = None
         else:
             self.flush()
         return self._layernorm(residual, y, w_post, weight, eps, rows, out_dtype, "layernorm")

@@ -125,7 +125,10 @@ def plain_logits(cfg, tensors, tokens):
     return plain.forward(cfg, tensors, tokens, torch.float64)
 
 
-LIMIT = {"float32": 3e-5, "bfloat16": 5e-2}
+# float32: only the order of summation differs. bfloat16: activations are rounded to 8 bits between the kernels and every sublayer
+# ends in a norm that brings its result back to full size, so the rounding of a dozen sublayers adds up to a few per cent of the
+# logits' spread (measured 0.03 to 0.05 at these sizes); a wrong key or a lost state moves them by 0.3 and more
+LIMIT = {"float32": 3e-5, "bfloat16": 1e-1}
 LENS = {"a": 150, "b": 67, "c": 41, "d": 9, "e": 118, "f": 2}
 
 
