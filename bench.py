@@ -843,13 +843,13 @@ def zepalorn_kernel_points(torch, pk) -> dict:
         qk = torch.randn(N, 2 * dh * dd + dh * dv, device=dev).to(bf) * 0.5
         a_, b_ = torch.randn(N, dh * dd, device=dev).to(bf), torch.randn(N, dh, device=dev).to(bf)
         A_log, dt_bias = torch.zeros(dh, device=dev), torch.full((dh * dd,), -3.0, device=dev)
-        state = torch.zeros(batch + 1, dh, dd, dv, device=dev)
+        state = torch.zeros(batch + 1, dh, dv, dd, device=dev)
         moved = batch * 2 * 4 * dh * dd * dv + N * (2 * (3 * dh * dd + dh * dv) + 4 * dh * dv)
         out[f"delta_rule_{what}_zepalorn"] = entry(_time(lambda: K.delta_rule(qk, dh, dh, dd, dv, a_, b_, 0, A_log, dt_bias, state, b), torch), moved, 8.0 * N * dh * dd * dv)
         xbc = torch.randn(N, sh * sv + 2 * sg * ns, device=dev).to(bf) * 0.5
         dt = torch.randn(N, sh, device=dev).to(bf)
         A2, bias2, skip = torch.zeros(sh, device=dev), torch.full((sh,), -3.0, device=dev), torch.ones(sh, device=dev)
-        state2 = torch.zeros(batch + 1, sh, ns, sv, device=dev)
+        state2 = torch.zeros(batch + 1, sh, sv, ns, device=dev)
         moved = batch * 2 * 4 * sh * ns * sv + N * (2 * (sh * sv + 2 * sg * ns) + 4 * sh * sv)
         out[f"state_space_{what}_zepalorn"] = entry(_time(lambda: K.ssm_scan(xbc, sh, sg, ns, sv, dt, 0, A2, bias2, skip, state2, b), torch), moved, 6.0 * N * sh * ns * sv)
         C = 2 * dh * dd + dh * dv
@@ -865,11 +865,11 @@ def zepalorn_kernel_points(torch, pk) -> dict:
         return K.layernorm(res, w, 1e-6, bf)
 
     out["norm_zepalorn"] = entry(_time(both, torch), N * W * (4 + 4 + 2 + 2))
-    # feed-forward going in: the tcgen05 product with SiLU in its epilogue against the library product + the clamped gated unit
+    # feed-forward going in: the tcgen05 product with SiLU in its epilogue against the same product with the clamped gated unit in it
     h = torch.randn(N, W, device=dev).to(bf)
     wgu = torch.randn(2 * ff, W, device=dev).to(bf) * 0.02
     out["ff_in_qwen2"] = entry(_time(lambda: K.gate_up_act(h, wgu, bf), torch), None, 2.0 * N * W * 2 * ff)
-    out["ff_in_zepalorn"] = entry(_time(lambda: K.glu_clamped(K.linear(h, wgu, transient=True), 7.0, 1.702, 1.0, bf), torch), None, 2.0 * N * W * 2 * ff)
+    out["ff_in_zepalorn"] = entry(_time(lambda: K.gate_up_act(h, wgu, bf, glu=(7.0, 1.702, 1.0)), torch), None, 2.0 * N * W * 2 * ff)
     # gated norms of the recurrences' results and the mean of the two halves of a side-by-side mixer (no counterpart in Qwen2)
     o, g = torch.randn(N, dh * dv, device=dev), torch.randn(N, dh * dv, device=dev).to(bf)
     nw = torch.ones(dv, device=dev)

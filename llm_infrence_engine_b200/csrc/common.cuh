@@ -109,6 +109,23 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 extern "C" int llmie_pdl_flag;  // 1: launch with the programmatic-serialization attribute (set by llmie_set_pdl)
 
+// A kernel that runs long and wants the whole device launches alone (`alone` = true): blocks that move in while the kernel before
+// still holds the multiprocessors go wherever room comes up first, several to one multiprocessor, and stay there.
+template <typename... KArgs, typename... Args>
+static inline int launch_kernel_on(bool alone, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (llmie_pdl_flag && !alone) ? 1 : 0;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 static inline int launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args... args) {
     cudaLaunchConfig_t cfg = {};

@@ -34,7 +34,7 @@ constexpr int EPI_THREADS = 128, THREADS = 64 + EPI_THREADS;
 
 template <int BN>
 __global__ void __launch_bounds__(THREADS) gateup_silu_tc_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                                                                  bf16* __restrict__ out, int M, int I, int K, int* error_flag) {
+                                                                  bf16* __restrict__ out, int M, int I, int K, int* error_flag, float limit, float alpha, float shift) {
     constexpr int B_BYTES = 2 * BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // BN gate rows and BN up rows per K step
     extern __shared__ unsigned char raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -138,8 +138,17 @@ __global__ void __launch_bounds__(THREADS) gateup_silu_tc_kernel(const __grid_co
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float g0 = __uint_as_float(gv[2 * j]), g1 = __uint_as_float(gv[2 * j + 1]);
-                    const float a = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(uv[2 * j]);
-                    const float b = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(uv[2 * j + 1]);
+                    float u0 = __uint_as_float(uv[2 * j]), u1 = __uint_as_float(uv[2 * j + 1]), a, b;
+                    if (limit > 0.f) {   // the clamped unit: min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift)
+                        const float c0 = fminf(g0, limit), c1 = fminf(g1, limit);
+                        u0 = fminf(fmaxf(u0, -limit), limit) + shift;
+                        u1 = fminf(fmaxf(u1, -limit), limit) + shift;
+                        a = __fdividef(c0, 1.0f + __expf(-alpha * c0)) * u0;
+                        b = __fdividef(c1, 1.0f + __expf(-alpha * c1)) * u1;
+                    } else {
+                        a = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+                        b = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                    }
                     const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
                     packed[j] = *reinterpret_cast<const uint32_t*>(&v);
                 }
@@ -184,7 +193,8 @@ inline int best_tile_width(long long m_tiles, int I, int blocks) {
 }
 
 template <int BN>
-int launch_gateup(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, cudaStream_t s) {
+int launch_gateup(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, float limit, float alpha,
+                  float shift, cudaStream_t s) {
     CUtensorMap mx, mw;
     int rc = tensor_map(x, M, K, BM, &mx);
     if (rc) return rc;
@@ -199,23 +209,30 @@ int launch_gateup(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, 
     }
     const long long tiles = (long long)((M + BM - 1) / BM) * ((I + BN - 1) / BN);
     const int grid = (int)(tiles < num_blocks ? tiles : num_blocks);
-    return launch_kernel(gateup_silu_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem, s, mx, mw, out, M, I, K, error_flag);
+    return launch_kernel(gateup_silu_tc_kernel<BN>, dim3(grid), dim3(THREADS), smem, s, mx, mw, out, M, I, K, error_flag, limit, alpha, shift);
 }
 
 }  // namespace
 
 // x [M, K] and w [2 I, K] bfloat16 row-major (K and I multiples of 8, bases 16-byte aligned), out bfloat16 [M, I].
 // num_blocks: the persistent grid (the number of multiprocessors; fewer if there are fewer tiles).
-LLMIE_API int llmie_gateup_silu_tc(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag,
+// limit > 0: the epilogue is min(g, limit) * sigmoid(alpha g) * (clamp(u, -limit, limit) + shift); limit <= 0: silu(g) * u.
+LLMIE_API int llmie_gateup_glu_tc(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag,
+                                   float limit, float alpha, float shift,
                                    cudaStream_t s) {
     if (M <= 0 || I <= 0) return 0;
     if (K <= 0 || K % 8 || I % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || !error_flag || num_blocks < 1)
         return LLMIE_ERR_BAD_ARGUMENT;
     switch (best_tile_width((M + BM - 1) / BM, I, num_blocks)) {
-        case 112: return launch_gateup<112>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        case 96: return launch_gateup<96>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        case 80: return launch_gateup<80>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        case 64: return launch_gateup<64>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        default: return launch_gateup<128>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 112: return launch_gateup<112>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        case 96: return launch_gateup<96>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        case 80: return launch_gateup<80>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        case 64: return launch_gateup<64>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        default: return launch_gateup<128>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
     }
+}
+
+// The same with silu(gate) * up as the epilogue.
+LLMIE_API int llmie_gateup_silu_tc(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, cudaStream_t s) {
+    return llmie_gateup_glu_tc(x, w, out, M, I, K, num_blocks, error_flag, 0.f, 1.f, 0.f, s);
 }

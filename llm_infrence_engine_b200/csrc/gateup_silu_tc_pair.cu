@@ -58,7 +58,7 @@ __device__ __forceinline__ void cluster_sync_all() {
 
 template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS) gateup_silu_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
-                                                                       bf16* __restrict__ out, int M, int I, int K, int* error_flag) {
+                                                                       bf16* __restrict__ out, int M, int I, int K, int* error_flag, float limit, float alpha, float shift) {
     constexpr int B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;   // this block's half of the weight rows of a K step
     extern __shared__ unsigned char raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~(uintptr_t)1023);
@@ -166,8 +166,17 @@ __global__ void __launch_bounds__(THREADS) gateup_silu_tc_pair_kernel(const __gr
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     const float g0 = __uint_as_float(gv[2 * j]), g1 = __uint_as_float(gv[2 * j + 1]);
-                    const float a = __fdividef(g0, 1.0f + __expf(-g0)) * __uint_as_float(uv[2 * j]);
-                    const float b = __fdividef(g1, 1.0f + __expf(-g1)) * __uint_as_float(uv[2 * j + 1]);
+                    float u0 = __uint_as_float(uv[2 * j]), u1 = __uint_as_float(uv[2 * j + 1]), a, b;
+                    if (limit > 0.f) {   // the clamped unit: min(g, limit) * sigmoid(alpha g) * (clamp(u) + shift)
+                        const float c0 = fminf(g0, limit), c1 = fminf(g1, limit);
+                        u0 = fminf(fmaxf(u0, -limit), limit) + shift;
+                        u1 = fminf(fmaxf(u1, -limit), limit) + shift;
+                        a = __fdividef(c0, 1.0f + __expf(-alpha * c0)) * u0;
+                        b = __fdividef(c1, 1.0f + __expf(-alpha * c1)) * u1;
+                    } else {
+                        a = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+                        b = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                    }
                     const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
                     packed[j] = *reinterpret_cast<const uint32_t*>(&v);
                 }
@@ -212,7 +221,8 @@ inline int best_tile_width(long long m_pairs, int I, int pairs_at_once) {
 }
 
 template <int BN>
-int launch_gateup_pair(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, cudaStream_t s) {
+int launch_gateup_pair(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, float limit, float alpha,
+                  float shift, cudaStream_t s) {
     constexpr int STAGES = BN > 96 ? 6 : 7;   // 32 KB (BN = 128) to 24 KB (BN = 64) per stage
     CUtensorMap mx, mw;
     int rc = tensor_map(x, M, K, BM, &mx);
@@ -242,22 +252,29 @@ int launch_gateup_pair(const bf16* x, const bf16* w, bf16* out, int M, int I, in
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = llmie_pdl_flag ? 2 : 1;
-    return (int)cudaLaunchKernelEx(&cfg, gateup_silu_tc_pair_kernel<BN, STAGES>, mx, mw, out, M, I, K, error_flag);
+    return (int)cudaLaunchKernelEx(&cfg, gateup_silu_tc_pair_kernel<BN, STAGES>, mx, mw, out, M, I, K, error_flag, limit, alpha, shift);
 }
 
 }  // namespace
 
 // As llmie_gateup_silu_tc, by pairs of blocks on tiles of 256 rows; num_blocks is rounded down to an even number.
-LLMIE_API int llmie_gateup_silu_tc_pair(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag,
+// limit > 0: the epilogue is min(g, limit) * sigmoid(alpha g) * (clamp(u, -limit, limit) + shift); limit <= 0: silu(g) * u.
+LLMIE_API int llmie_gateup_glu_tc_pair(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag,
+                                        float limit, float alpha, float shift,
                                         cudaStream_t s) {
     if (M <= 0 || I <= 0) return 0;
     if (K <= 0 || K % 8 || I % 8 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || !error_flag || num_blocks < 2)
         return LLMIE_ERR_BAD_ARGUMENT;
     switch (best_tile_width(((M + BM - 1) / BM + 1) / 2, I, num_blocks / 2)) {
-        case 112: return launch_gateup_pair<112>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        case 96: return launch_gateup_pair<96>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        case 80: return launch_gateup_pair<80>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        case 64: return launch_gateup_pair<64>(x, w, out, M, I, K, num_blocks, error_flag, s);
-        default: return launch_gateup_pair<128>(x, w, out, M, I, K, num_blocks, error_flag, s);
+        case 112: return launch_gateup_pair<112>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        case 96: return launch_gateup_pair<96>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        case 80: return launch_gateup_pair<80>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        case 64: return launch_gateup_pair<64>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
+        default: return launch_gateup_pair<128>(x, w, out, M, I, K, num_blocks, error_flag, limit, alpha, shift, s);
     }
+}
+
+// The same with silu(gate) * up as the epilogue.
+LLMIE_API int llmie_gateup_silu_tc_pair(const bf16* x, const bf16* w, bf16* out, int M, int I, int K, int num_blocks, int* error_flag, cudaStream_t s) {
+    return llmie_gateup_glu_tc_pair(x, w, out, M, I, K, num_blocks, error_flag, 0.f, 1.f, 0.f, s);
 }

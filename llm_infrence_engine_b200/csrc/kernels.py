@@ -106,8 +106,10 @@ class CudaKernels:
                    "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
-        self._gate_up_cluster = self._gate_up_pair = None
-        for attr, name in (("_gate_up_cluster", "llmie_gateup_silu_tc_cluster"), ("_gate_up_pair", "llmie_gateup_silu_tc_pair")):
+        self._gate_up_cluster = self._gate_up_pair = self._gate_up_glu_pair = None
+        self.lib.llmie_gateup_glu_tc.restype = ctypes.c_int
+        for attr, name in (("_gate_up_cluster", "llmie_gateup_silu_tc_cluster"), ("_gate_up_pair", "llmie_gateup_silu_tc_pair"),
+                           ("_gate_up_glu_pair", "llmie_gateup_glu_tc_pair")):
             try:
                 fn = getattr(self.lib, name)
                 fn.restype = ctypes.c_int
@@ -293,7 +295,19 @@ class CudaKernels:
         ``add_to``: a float32 ``[rows, outputs]`` tensor (the residual stream) that the product is added into;
         nothing is returned. ``transient``: the caller hands the result straight to ``rope_kv_write`` or ``silu_mul``
         and nowhere else; for small bfloat16 batches it is then a float32 view of the library's accumulation buffer,
-        which those kernels read and set back to zero."""
+        which those kernels read and set back to zero. ``x`` may be a run of columns of wider rows (unit column stride): the
+        library product takes it as it is, every other path gets a copy."""
+        if x.dim() == 2 and not x.is_contiguous():
+            as_it_is = (x.stride(1) == 1 and x.dtype == torch.bfloat16 and self.use_cublas and add_to is None and not transient
+                        and (out_dtype or x.dtype) == torch.bfloat16 and x.data_ptr() % 16 == 0 and x.stride(0) % 8 == 0)
+            if as_it_is:
+                self._need(w, "w", x.dtype, 2)
+                if x.shape[1] != w.shape[1]:
+                    raise KernelError(f"linear: x has {x.shape[1]} columns, w has {w.shape[1]}")
+                self.launches += 1
+                return torch.nn.functional.linear(x, w)
+            x = x.contiguous()
+            self.launches += 1
         self._need(x, "x", None, 2)
         M, K = x.shape
         N = w.shape[0]
@@ -710,11 +724,15 @@ class CudaKernels:
         return self.paged_attention(qkv, k_pool, v_pool, block_table, token_seq, positions, num_heads, num_kv_heads, head_dim, page_size,
                                     scale, window, max_context, batch=batch)
 
-    def gate_up_act(self, x, w_gate_up, out_dtype=None):
+    def gate_up_act(self, x, w_gate_up, out_dtype=None, glu=None):
         """``silu(x Wg^T) * (x Wu^T)`` for the fused matrix ``w_gate_up`` ``[2 I, K]`` (gate rows first). Prompt portions in
         bfloat16 take one tcgen05 kernel whose epilogue is the activation (the float32 sums stay in tensor memory; nothing of
-        width 2 I is written); everything else is the product followed by ``silu_mul``."""
+        width 2 I is written); everything else is the product followed by ``silu_mul``. ``glu = (limit, alpha, shift)`` asks for
+        the clamped unit ``g sigmoid(alpha g) (u + shift)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` instead."""
         out_dtype = out_dtype or x.dtype
+        limit, alpha, shift = (float(v) for v in glu) if glu is not None else (0.0, 1.0, 0.0)
+        if glu is not None and not limit > 0:
+            raise KernelError("gate_up_act: the clamped unit needs a positive limit")
         M, K_ = x.shape
         if (self.use_tc_gate_up and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and M > self.tc_max_rows and K_ % 8 == 0
                 and w_gate_up.dim() == 2 and w_gate_up.shape[0] % 16 == 0 and w_gate_up.shape[1] == K_ and x.is_contiguous()
@@ -724,13 +742,21 @@ class CudaKernels:
             # three forms of the kernel: one block per tile of 128 rows; pairs of multiprocessors on tiles of 256 rows
             # (cta_group::2), the default for long portions; pairs of blocks that share their weight rows by TMA multicast,
             # where the library was built with that optional source file (off by default: measured no faster)
-            fn = self._gate_up_cluster if (self.use_cluster_gate_up and M > 128) else None
-            if self.use_pair_gate_up and self._gate_up_pair is not None and M >= self.pair_gate_up_min_rows:
+            fn = self._gate_up_cluster if (self.use_cluster_gate_up and M > 128 and glu is None) else None
+            pair = self.use_pair_gate_up and self._gate_up_pair is not None and M >= self.pair_gate_up_min_rows
+            if pair and glu is None:
                 fn = self._gate_up_pair
-            fn = fn or self.lib.llmie_gateup_silu_tc
-            self._check(fn(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K_, self.num_sms, _ptr(self._errors(x.device)), self._stream()),
-                        "gate_up_act (tcgen05)")
+            if fn is not None or glu is None:
+                fn = fn or self.lib.llmie_gateup_silu_tc
+                self._check(fn(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K_, self.num_sms, _ptr(self._errors(x.device)), self._stream()),
+                            "gate_up_act (tcgen05)")
+                return out
+            fn = self._gate_up_glu_pair if (pair and self._gate_up_glu_pair is not None) else self.lib.llmie_gateup_glu_tc
+            self._check(fn(_ptr(x), _ptr(w_gate_up), _ptr(out), M, I, K_, self.num_sms, _ptr(self._errors(x.device)), ctypes.c_float(limit),
+                           ctypes.c_float(alpha), ctypes.c_float(shift), self._stream()), "gate_up_act (tcgen05, clamped unit)")
             return out
+        if glu is not None:
+            return self.glu_clamped(self.linear(x, w_gate_up, transient=True), limit, alpha, shift, out_dtype)
         return self.silu_mul(self.linear(x, w_gate_up, transient=True), out_dtype)
 
     def silu_mul(self, gu, out_dtype=None):
@@ -1003,8 +1029,8 @@ class CudaKernels:
             if w_post.shape[0] != H:
                 raise KernelError(f"{what}: the post-norm's weight has {w_post.shape[0]} elements, rows have {H}")
             clear = self._clears(y)
-        if H > 50000:
-            raise KernelError(f"{what}: rows of {H} elements do not fit the kernel's shared memory (at most 50000)")
+        if H > 12500:
+            raise KernelError(f"{what}: rows of {H} elements do not fit the kernel's shared memory (at most 12500)")
         out = None
         out_dt = y_dt
         n_out = N if rows is None else rows.shape[0]
@@ -1155,7 +1181,8 @@ class CudaKernels:
         return out
 
     def delta_rule(self, qkv, num_heads, num_kv_heads, head_dim, v_head_dim, a, b, b_col, A_log, dt_bias, state, batch, unit_eps=1e-6):
-        """The gated delta rule with a decay per key channel over the rows of each request, from ``state [slots, heads, head_dim, v_head_dim]``:
+        """The gated delta rule with a decay per key channel over the rows of each request, from ``state [slots, heads, v_head_dim, head_dim]``
+        (a head's ``S [head_dim, v_head_dim]`` kept column by column):
         ``qkv = [q: kv_heads x head_dim | k: the same | v: heads x v_head_dim]`` (after convolution and activation), ``a [N, heads * head_dim]``
         the decay's logits, ``b`` (columns from ``b_col``) the logits of beta. Returns float32 ``[N, heads * v_head_dim]``."""
         self._need(qkv, "qkv", None, 2)
@@ -1167,8 +1194,8 @@ class CudaKernels:
             raise KernelError("delta_rule: the rows do not fit the head sizes (head_dim at most 256)")
         if b.dim() != 2 or b.stride(1) != 1 or b.dtype != qkv.dtype or b_col + H > b.shape[1]:
             raise KernelError("delta_rule: the beta logits must be columns of rows of the same type")
-        if tuple(state.shape[1:]) != (H, D, DV):
-            raise KernelError(f"delta_rule: state is {list(state.shape)}, expected [slots, {H}, {D}, {DV}]")
+        if tuple(state.shape[1:]) != (H, DV, D):
+            raise KernelError(f"delta_rule: state is {list(state.shape)}, expected [slots, {H}, {DV}, {D}]")
         self._need(A_log, "A_log", torch.float32, 1)
         self._need(dt_bias, "dt_bias", torch.float32, 1)
         dev = qkv.device
@@ -1176,23 +1203,23 @@ class CudaKernels:
         flat = work.view(-1)
         o = 0
         pieces = []
-        for n in (N * G * D, N * G * D, N * G, N * H * D, N * H):
+        for n in (N * G * D, N * G * D, N * H * D, N * G, N * H):   # (rows of head_dim floats first: they start on 16-byte boundaries)
             pieces.append(flat[o:o + n])
             o += n
-        qn, kn, kq, decay, beta = pieces
+        qn, kn, decay, kq, beta = pieces
         dt = self._dt(qkv, "qkv")
         self._check(self.lib.llmie_delta_prepare(_ptr(qkv), qkv.shape[1], 0, G * D, _ptr(a), a.shape[1], ctypes.c_void_p(b.data_ptr() + b_col * b.element_size()),
                                                  b.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(qn), _ptr(kn), _ptr(kq), _ptr(decay), _ptr(beta), N, H, G, D,
                                                  ctypes.c_float(D ** -0.5), ctypes.c_float(unit_eps), dt, self._stream()), "delta_rule (prepare)")
         out = torch.empty((N, H * DV), dtype=torch.float32, device=dev)
         self._check(self.lib.llmie_delta_scan(_ptr(qkv), qkv.shape[1], 2 * G * D, _ptr(qn), _ptr(kn), _ptr(kq), _ptr(decay), _ptr(beta), _ptr(state),
-                                              _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(out), H, G, D, DV, batch.num_seqs, dt, self._stream()),
-                    "delta_rule (scan)")
+                                              _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots), _ptr(out), H, G, D, DV, batch.num_seqs, batch.max_seq_len, dt,
+                                              self._stream()), "delta_rule (scan)")
         return out
 
     def ssm_scan(self, xbc, num_heads, groups, state_size, v_head_dim, dt, dt_col, A_log, dt_bias, skip, state, batch):
-        """The state-space recurrence with one decay per head over the rows of each request, from ``state [slots, heads, state_size,
-        v_head_dim]``: ``xbc = [x: heads x v_head_dim | B: groups x state_size | C: the same]`` (after convolution and activation), ``dt``
+        """The state-space recurrence with one decay per head over the rows of each request, from ``state [slots, heads, v_head_dim,
+        state_size]`` (a head's ``S [state_size, v_head_dim]`` kept column by column): ``xbc = [x: heads x v_head_dim | B: groups x state_size | C: the same]`` (after convolution and activation), ``dt``
         (columns from ``dt_col``) the step sizes' logits. Returns float32 ``[N, heads * v_head_dim]``."""
         self._need(xbc, "xbc", None, 2)
         self._need(state, "state", torch.float32, 4)
@@ -1201,8 +1228,8 @@ class CudaKernels:
             raise KernelError("ssm_scan: the rows do not fit the head sizes (state size at most 256)")
         if dt.dim() != 2 or dt.stride(1) != 1 or dt.dtype != xbc.dtype or dt_col + H > dt.shape[1]:
             raise KernelError("ssm_scan: the step sizes must be columns of rows of the same type")
-        if tuple(state.shape[1:]) != (H, NS, DV):
-            raise KernelError(f"ssm_scan: state is {list(state.shape)}, expected [slots, {H}, {NS}, {DV}]")
+        if tuple(state.shape[1:]) != (H, DV, NS):
+            raise KernelError(f"ssm_scan: state is {list(state.shape)}, expected [slots, {H}, {DV}, {NS}]")
         for name, t in (("A_log", A_log), ("dt_bias", dt_bias), ("skip", skip)):
             self._need(t, name, torch.float32, 1)
             if t.shape[0] != H:
@@ -1210,7 +1237,7 @@ class CudaKernels:
         out = torch.empty((xbc.shape[0], H * DV), dtype=torch.float32, device=xbc.device)
         self._check(self.lib.llmie_ssm_scan(_ptr(xbc), xbc.shape[1], 0, H * DV, H * DV + G * NS, ctypes.c_void_p(dt.data_ptr() + dt_col * dt.element_size()),
                                             dt.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(skip), _ptr(state), _ptr(batch.seq_starts_dev), _ptr(batch.seq_slots),
-                                            _ptr(out), H, G, NS, DV, batch.num_seqs, self._dt(xbc, "xbc"), self._stream()), "ssm_scan")
+                                            _ptr(out), H, G, NS, DV, batch.num_seqs, batch.max_seq_len, self._dt(xbc, "xbc"), self._stream()), "ssm_scan")
         return out
 
     # ------------------------------------------------------------------ latent attention

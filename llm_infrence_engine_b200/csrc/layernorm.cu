@@ -1,7 +1,7 @@
 // Layer norm with a weight and no bias, for blocks that norm a sublayer's input AND its result:
 //   x <- x + LN_post(y);  h = LN_pre(x)
 // One kernel does either half or both, one block per row, the row in shared memory between the passes. Mean, variance
-// (the mean of the squared deviations, taken in a second pass) and the scaling are 32-bit. Also here: the root-mean-square
+// (the mean of the squared deviations, taken in a second pass about the finished mean) and the scaling are 32-bit. Also here: the root-mean-square
 // norm over groups of a row with a gate, and the mean of several rows each divided by its root mean square.
 #include <math.h>
 
@@ -15,61 +15,96 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 // y (of type TY, or null): the sublayer's result whose layer norm (weight w_post) is added to x first; with clear_y the row of
 // y is set to zero behind the read (it is then a float buffer that the next sublayer adds into).
 // w_pre (or null): out[blockIdx.x] = LN(x) * w_pre in type TO.
-template <typename TY, typename TO>
+// Mean and reciprocal standard deviation of the H floats of buf, in two passes (the squared deviations are taken about the
+// finished mean); every thread gets both. A thread reads the entries it wrote itself, so no barrier is needed before.
+template <int VEC>
+__device__ __forceinline__ void row_stats(const float* buf, int H, int step, float eps, float* scratch, float& mean, float& rstd) {
+    float sum = 0.f;
+    for (int i = threadIdx.x * VEC; i < H; i += step)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) sum += buf[i + j];
+    mean = block_sum(sum, scratch) / (float)H;
+    float sq = 0.f;
+    for (int i = threadIdx.x * VEC; i < H; i += step)
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) { const float d = buf[i + j] - mean; sq = fmaf(d, d, sq); }
+    rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+}
+
+template <typename TY, typename TO, int VEC>
 __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, const float* __restrict__ w_post, int clear_y,
                                  const float* __restrict__ w_pre, TO* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
-    extern __shared__ __align__(16) float ln_buf[];   // H floats of the row, 36 for the reductions
-    float* scratch = ln_buf + H;
+    extern __shared__ __align__(16) float ln_buf[];   // the row of x, the row of y, both weights (H floats each), 100 for the reductions
+    float* x_buf = ln_buf;
+    float* y_buf = x_buf + H;
+    float* wp_buf = y_buf + H;
+    float* wq_buf = wp_buf + H;
+    float* scratch = wq_buf + H;
+    const int step = blockDim.x * VEC;
     pdl_trigger();
+    // the weights do not depend on the kernel before: they are fetched before the wait
+    for (int i = threadIdx.x * VEC; i < H; i += step) {
+        if constexpr (VEC == 4) {
+            if (w_post) *reinterpret_cast<float4*>(wp_buf + i) = *reinterpret_cast<const float4*>(w_post + i);
+            if (w_pre) *reinterpret_cast<float4*>(wq_buf + i) = *reinterpret_cast<const float4*>(w_pre + i);
+        } else {
+            if (w_post) wp_buf[i] = w_post[i];
+            if (w_pre) wq_buf[i] = w_pre[i];
+        }
+    }
     pdl_wait();
     const int r = rows ? rows[blockIdx.x] : blockIdx.x;
     float* xr = x + (size_t)r * H;
-    if (y) {
-        TY* yr = y + (size_t)r * H;
-        float sum = 0.f;
-        for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float v = to_f32(yr[i]);
-            ln_buf[i] = v;
-            sum += v;
-            if (clear_y) yr[i] = from_f32<TY>(0.f);
+    TY* yr = y ? y + (size_t)r * H : nullptr;
+    // both rows are asked for at once: one trip to memory
+    for (int i = threadIdx.x * VEC; i < H; i += step) {
+        float v[VEC], u[VEC];
+        if constexpr (VEC == 4) load4(xr + i, v); else v[0] = xr[i];
+        if (yr) { if constexpr (VEC == 4) load4(yr + i, u); else u[0] = to_f32(yr[i]); }
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) { x_buf[i + j] = v[j]; if (yr) y_buf[i + j] = u[j]; }
+        if (yr && clear_y) {
+            const float zero[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (VEC == 4) store4(yr + i, zero); else yr[i] = from_f32<TY>(0.f);
         }
-        const float mean = block_sum(sum, scratch) / (float)H;
-        float sq = 0.f;
-        for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float d = ln_buf[i] - mean;
-            sq = fmaf(d, d, sq);
+    }
+    if (yr) {
+        float mean, rstd;
+        row_stats<VEC>(y_buf, H, step, eps, scratch, mean, rstd);
+        for (int i = threadIdx.x * VEC; i < H; i += step) {
+            float v[VEC];
+#pragma unroll
+            for (int j = 0; j < VEC; ++j) { v[j] = x_buf[i + j] + (y_buf[i + j] - mean) * rstd * wp_buf[i + j]; x_buf[i + j] = v[j]; }
+            if (!rows) { if constexpr (VEC == 4) store4(xr + i, v); else xr[i] = v[0]; }
         }
-        const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
-        for (int i = threadIdx.x; i < H; i += blockDim.x) {
-            const float v = xr[i] + (ln_buf[i] - mean) * rstd * w_post[i];
-            ln_buf[i] = v;
-            if (!rows) xr[i] = v;
-        }
-    } else {
-        for (int i = threadIdx.x; i < H; i += blockDim.x) ln_buf[i] = xr[i];
     }
     if (!w_pre) return;
-    float sum = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) sum += ln_buf[i];   // a thread reads back what it wrote itself
-    const float mean = block_sum(sum, scratch) / (float)H;
-    float sq = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float d = ln_buf[i] - mean;
-        sq = fmaf(d, d, sq);
-    }
-    const float rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
+    float mean, rstd;
+    row_stats<VEC>(x_buf, H, step, eps, scratch, mean, rstd);
     TO* o = out + (size_t)blockIdx.x * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((ln_buf[i] - mean) * rstd * w_pre[i]);
+    for (int i = threadIdx.x * VEC; i < H; i += step) {
+        float v[VEC];
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) v[j] = (x_buf[i + j] - mean) * rstd * wq_buf[i + j];
+        if constexpr (VEC == 4) store4(o + i, v); else o[i] = from_f32<TO>(v[0]);
+    }
 }
 
 template <typename TY, typename TO>
 int launch_layernorm(float* x, void* y, const float* w_post, int clear_y, const float* w_pre, void* out, const int* rows, int n_out,
                      int H, float eps, cudaStream_t s) {
-    const size_t smem = (size_t)(H + 36) * sizeof(float);
+    const size_t smem = (size_t)(4 * H + 100) * sizeof(float);
+    const bool vec = H % 4 == 0 && ((uintptr_t)x % 16 == 0) && ((uintptr_t)y % 16 == 0) && ((uintptr_t)out % 16 == 0) &&
+                     ((uintptr_t)w_post % 16 == 0) && ((uintptr_t)w_pre % 16 == 0);
+    const int per = vec ? 4 : 1;
     int threads = 32;
-    while (threads < 512 && threads * 4 <= H) threads *= 2;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    return launch_kernel(layernorm_kernel<TY, TO>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, (TO*)out, rows, H, eps);
+    while (threads < 512 && threads * per * 2 <= H) threads *= 2;
+    if (vec) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return launch_kernel(layernorm_kernel<TY, TO, 4>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, (TO*)out, rows, H, eps);
+    }
+    if (smem > 48 * 1024) cudaFuncSetAttribute(layernorm_kernel<TY, TO, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    return launch_kernel(layernorm_kernel<TY, TO, 1>, dim3(n_out), dim3(threads), smem, s, x, (TY*)y, w_post, clear_y, w_pre, (TO*)out, rows, H, eps);
 }
 
 // Root-mean-square norm over groups of `gs` consecutive channels, with a gate, one block per (row, group):
@@ -100,6 +135,46 @@ __global__ void group_rmsnorm_gate_kernel(const float* __restrict__ x, const TG*
         v = v * rstd * w[(c0 + i) % w_len];
         if (mode == 1) v *= sigmoid_f(z);
         o[i] = from_f32<TO>(v);
+    }
+}
+
+// The same for groups of up to 256 channels: a warp per (row, group), the group's values in registers, no barrier.
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(128) group_rmsnorm_gate_warp_kernel(const float* __restrict__ x, const TG* __restrict__ gate, int gate_stride,
+                                                                      const float* __restrict__ w, int w_len, TO* __restrict__ out, int N, int C,
+                                                                      int gs, float eps, int mode) {
+    pdl_trigger();
+    pdl_wait();
+    const int groups = C / gs;
+    const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (item >= (long long)N * groups) return;
+    const int n = (int)(item / groups), c0 = (int)(item % groups) * gs;
+    const float* xr = x + (size_t)n * C + c0;
+    const TG* gr = gate + (size_t)n * gate_stride + c0;
+    float v[8], z[8];   // gs <= 256
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int i = lane + 32 * k;
+        v[k] = 0.f; z[k] = 0.f;
+        if (i < gs) {
+            v[k] = xr[i];
+            z[k] = to_f32(gr[i]);
+            if (mode == 0) v[k] *= z[k] / (1.0f + expf(-z[k]));
+            sq = fmaf(v[k], v[k], sq);
+        }
+    }
+    const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)gs + eps);
+    TO* o = out + (size_t)n * C + c0;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        const int i = lane + 32 * k;
+        if (i < gs) {
+            float r = v[k] * rstd * w[(c0 + i) % w_len];
+            if (mode == 1) r *= sigmoid_f(z[k]);
+            o[i] = from_f32<TO>(r);
+        }
     }
 }
 
@@ -135,7 +210,7 @@ __global__ void dual_rmsnorm_mix_kernel(TA* __restrict__ a, TB* __restrict__ b, 
 LLMIE_API int llmie_layernorm(float* x, void* y, int y_dtype, const float* w_post, int clear_y, const float* w_pre, void* out,
                               int out_dtype, const int* rows, int n_out, int H, float eps, cudaStream_t s) {
     if (n_out <= 0) return 0;
-    if (H <= 0 || (size_t)(H + 36) * sizeof(float) > 200 * 1024 || (y && !w_post) || (w_pre && !out)) return LLMIE_ERR_BAD_ARGUMENT;
+    if (H <= 0 || (size_t)(4 * H + 100) * sizeof(float) > 200 * 1024 || (y && !w_post) || (w_pre && !out)) return LLMIE_ERR_BAD_ARGUMENT;
     if (y_dtype == DT_F32 && out_dtype == DT_F32) return launch_layernorm<float, float>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
     if (y_dtype == DT_F32 && out_dtype == DT_BF16) return launch_layernorm<float, bf16>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
     if (y_dtype == DT_BF16 && out_dtype == DT_BF16) return launch_layernorm<bf16, bf16>(x, y, w_post, clear_y, w_pre, out, rows, n_out, H, eps, s);
@@ -149,8 +224,15 @@ LLMIE_API int llmie_group_rmsnorm_gate(const float* x, const void* gate, int gat
     int threads = 32;
     while (threads < 256 && threads * 2 <= gs) threads *= 2;
     const dim3 grid(N, C / gs);
-#define LLMIE_GRG(TG, TO) return launch_kernel(group_rmsnorm_gate_kernel<TG, TO>, grid, dim3(threads), 0, s, x, (const TG*)gate, gate_stride, w, w_len, \
-                                               (TO*)out, C, gs, eps, mode)
+    const long long items = (long long)N * (C / gs);
+#define LLMIE_GRG(TG, TO)                                                                                                                        \
+    {                                                                                                                                            \
+        if (gs <= 256)   /* (the registers of a lane hold gs / 32 values: beyond 256 the block form is the better one) */                      \
+            return launch_kernel(group_rmsnorm_gate_warp_kernel<TG, TO>, dim3((unsigned)((items + 3) / 4)), dim3(128), 0, s, x, (const TG*)gate, \
+                                 gate_stride, w, w_len, (TO*)out, N, C, gs, eps, mode);                                                          \
+        return launch_kernel(group_rmsnorm_gate_kernel<TG, TO>, grid, dim3(threads), 0, s, x, (const TG*)gate, gate_stride, w, w_len, (TO*)out,  \
+                             C, gs, eps, mode);                                                                                                  \
+    }
     if (gate_dtype == DT_F32 && out_dtype == DT_F32) LLMIE_GRG(float, float);
     if (gate_dtype == DT_BF16 && out_dtype == DT_BF16) LLMIE_GRG(bf16, bf16);
 #undef LLMIE_GRG

@@ -130,142 +130,311 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(const T* __restrict_
 }
 
 // ------------------------------------------------------------------------------------------------
-// The gated delta rule. Per head, S is [D, DV]; for every token, in order:
-//   S <- decay (.) S (row d by decay[d]);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
-// The columns of S are independent of one another: a warp owns 32 of them, a lane one column, all D entries in registers.
-// With S' = decay (.) S both products of a token are taken from S' in one pass over the registers: r = S'^T k and
-// S'^T q, and then o = S'^T q + u (k . q), the last factor coming with the token. Tokens arrive in tiles through shared memory.
+// How both recurrences are laid out. Per head the state S is [D, DV] (D: key channels or state size). Its columns are
+// independent of one another, and within a column a token's work is a sum over D, which sets the length of the chain from one
+// token to the next: so PARTS lanes share a column (a whole warp for D of 128 and more), lane part j holding the entries
+// d = 4 PARTS i + 4 j + c (c < 4) in registers; a warp owns 32 / PARTS columns, a block of eight warps 8 times that; a token
+// costs D / PARTS steps per lane plus log2(PARTS) shuffles per sum. In memory a state is kept column by column ([DV][D]), so
+// that a lane's entries are 16-byte pieces and a column's lanes read one contiguous run. Tokens arrive in tiles of SCAN_TILE
+// through a two-stage ring in shared memory (the next tile lands while this one is worked on; rows padded with zeros to DMAX;
+// the parts of a step read contiguous 16-byte pieces: no bank conflict), and with them the block's columns of the token's
+// own input. The order of every sum is fixed by D alone, so a result does not depend on how many rows a step brings.
 constexpr int SCAN_TILE = 8;
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_ALONE_ROWS = 64;   // steps whose longest request brings this many rows launch the scans alone
 
+template <int DMAX> struct ScanParts { static constexpr int value = DMAX >= 128 ? 32 : DMAX / 4; };
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src));
+}
+__device__ __forceinline__ void cp_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+template <int PARTS> __device__ __forceinline__ float parts_sum(float v) {
+#pragma unroll
+    for (int o = 1; o < PARTS; o <<= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// rows of `count` tokens, each D floats at src + (first + t) * stride, into dst[t][DMAX] (zeros beyond D)
+template <int DMAX>
+__device__ __forceinline__ void fetch_rows(float* dst, const float* __restrict__ src, size_t stride, int count, int D, bool vec) {
+    constexpr int Q = DMAX / 4;
+    for (int i = threadIdx.x; i < count * Q; i += SCAN_THREADS) {
+        const int t = i / Q, d = (i % Q) * 4;
+        float* o = dst + t * DMAX + d;
+        const float* p = src + (size_t)t * stride + d;
+        if (vec && d < D) {
+            cp_async16(o, p);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) o[c] = d + c < D ? p[c] : 0.f;
+        }
+    }
+}
+
+// a lane's entries of its column of the state, from / to st[D] (the column's run in memory)
+template <int DPL, int PARTS>
+__device__ __forceinline__ void load_column(float* S, const float* st, int part, int D, bool live, bool vec) {
+#pragma unroll
+    for (int i = 0; i < DPL / 4; ++i) {
+        const int d = 4 * PARTS * i + 4 * part;
+        if (live && vec && d < D) {
+            const float4 v = *reinterpret_cast<const float4*>(st + d);
+            S[4 * i] = v.x; S[4 * i + 1] = v.y; S[4 * i + 2] = v.z; S[4 * i + 3] = v.w;
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) S[4 * i + c] = (live && d + c < D) ? st[d + c] : 0.f;
+        }
+    }
+}
+template <int DPL, int PARTS>
+__device__ __forceinline__ void store_column(const float* S, float* st, int part, int D, bool vec) {
+#pragma unroll
+    for (int i = 0; i < DPL / 4; ++i) {
+        const int d = 4 * PARTS * i + 4 * part;
+        if (vec && d < D) {
+            *reinterpret_cast<float4*>(st + d) = make_float4(S[4 * i], S[4 * i + 1], S[4 * i + 2], S[4 * i + 3]);
+        } else {
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                if (d + c < D) st[d + c] = S[4 * i + c];
+        }
+    }
+}
+
+// The gated delta rule. For every token, in order:
+//   S <- decay (.) S (row d by decay[d]);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+// With S' = decay (.) S both products of a token are taken from S' in one pass over the registers: r = S'^T k and S'^T q, and
+// then o = S'^T q + u (k . q), the last factor coming with the token.
 template <typename T, int DMAX>
-__global__ void __launch_bounds__(32) delta_scan_kernel(const T* __restrict__ v, int v_stride, int v_col, const float* __restrict__ qn,
-                                                        const float* __restrict__ kn, const float* __restrict__ kq,
-                                                        const float* __restrict__ decay, const float* __restrict__ beta,
-                                                        float* __restrict__ state, const int* __restrict__ seq_starts,
-                                                        const int* __restrict__ seq_slots, float* __restrict__ out, int H, int G, int D,
-                                                        int DV) {
-    __shared__ __align__(16) float k_s[SCAN_TILE][DMAX], q_s[SCAN_TILE][DMAX], g_s[SCAN_TILE][DMAX];
-    __shared__ float beta_s[SCAN_TILE], kq_s[SCAN_TILE];
-    pdl_trigger();
+__global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(const T* __restrict__ v, int v_stride, int v_col, const float* __restrict__ qn,
+                                                                  const float* __restrict__ kn, const float* __restrict__ kq,
+                                                                  const float* __restrict__ decay, const float* __restrict__ beta,
+                                                                  float* __restrict__ state, const int* __restrict__ seq_starts,
+                                                                  const int* __restrict__ seq_slots, float* __restrict__ out, int H, int G,
+                                                                  int D, int DV) {
+    constexpr int PARTS = ScanParts<DMAX>::value, DPL = DMAX / PARTS, COLS = SCAN_THREADS / PARTS;
+    extern __shared__ __align__(16) float scan_smem[];
+    float* k_s = scan_smem;                              // [2][SCAN_TILE][DMAX]
+    float* q_s = k_s + 2 * SCAN_TILE * DMAX;
+    float* g_s = q_s + 2 * SCAN_TILE * DMAX;
+    float* beta_s = g_s + 2 * SCAN_TILE * DMAX;          // [2][SCAN_TILE]
+    float* kq_s = beta_s + 2 * SCAN_TILE;
+    float* v_s = kq_s + 2 * SCAN_TILE;                   // [2][SCAN_TILE][COLS]
     pdl_wait();
-    const int lane = threadIdx.x;
-    const int col = blockIdx.x * 32 + lane;
+    const int part = threadIdx.x % PARTS;
+    const int col = blockIdx.x * COLS + threadIdx.x / PARTS;
     const int h = blockIdx.y, r = blockIdx.z;
     const int g = h / (H / G);
     const bool live = col < DV;
+    const bool vec = (D & 3) == 0;
     const int s0 = seq_starts[r], s1 = seq_starts[r + 1];
-    float* st = state + (((size_t)seq_slots[r] * H + h) * D) * DV + col;
-    float S[DMAX];
-#pragma unroll
-    for (int d = 0; d < DMAX; ++d) S[d] = (live && d < D) ? st[(size_t)d * DV] : 0.f;
-    for (int base = s0; base < s1; base += SCAN_TILE) {
+    float* st = state + (((size_t)seq_slots[r] * H + h) * DV + (live ? col : 0)) * D;
+    float S[DPL];
+    load_column<DPL, PARTS>(S, st, part, D, live, vec);
+    auto fetch = [&](int base, int buf) {   // the rows of a tile: asynchronous copies
         const int count = min(SCAN_TILE, s1 - base);
-        __syncwarp();
-        for (int i = lane; i < count * DMAX; i += 32) {
-            const int t = i / DMAX, d = i % DMAX;
-            const int n = base + t;
-            const bool in = d < D;
-            k_s[t][d] = in ? kn[((size_t)n * G + g) * D + d] : 0.f;
-            q_s[t][d] = in ? qn[((size_t)n * G + g) * D + d] : 0.f;
-            g_s[t][d] = in ? decay[((size_t)n * H + h) * D + d] : 0.f;
+        fetch_rows<DMAX>(k_s + buf * SCAN_TILE * DMAX, kn + ((size_t)base * G + g) * D, (size_t)G * D, count, D, vec);
+        fetch_rows<DMAX>(q_s + buf * SCAN_TILE * DMAX, qn + ((size_t)base * G + g) * D, (size_t)G * D, count, D, vec);
+        fetch_rows<DMAX>(g_s + buf * SCAN_TILE * DMAX, decay + ((size_t)base * H + h) * D, (size_t)H * D, count, D, vec);
+    };
+    // A tile's numbers per token (beta, k . q) and the block's columns of v: loaded into registers a tile ahead, put into shared
+    // memory after the tile's work, so that nobody waits for them. Thread i < SCAN_TILE holds token i's two numbers; the
+    // threads from the end backwards hold v, VPT values each.
+    constexpr int VPT = (SCAN_TILE * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
+    float pre_beta = 0.f, pre_kq = 0.f, pre_v[VPT];
+    auto load_small = [&](int base) {
+        const int count = min(SCAN_TILE, s1 - base);
+        if (threadIdx.x < count) {
+            pre_beta = beta[(size_t)(base + threadIdx.x) * H + h];
+            pre_kq = kq[(size_t)(base + threadIdx.x) * G + g];
         }
-        if (lane < count) {
-            beta_s[lane] = beta[(size_t)(base + lane) * H + h];
-            kq_s[lane] = kq[(size_t)(base + lane) * G + g];
-        }
-        __syncwarp();
-        for (int t = 0; t < count; ++t) {
-            const int n = base + t;
-            const float vv = live ? to_f32(v[(size_t)n * v_stride + v_col + h * DV + col]) : 0.f;
-            float rk = 0.f, rq = 0.f;
 #pragma unroll
-            for (int d = 0; d < DMAX; d += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&k_s[t][d]);
-                const float4 q4 = *reinterpret_cast<const float4*>(&q_s[t][d]);
-                const float4 g4 = *reinterpret_cast<const float4*>(&g_s[t][d]);
-                S[d] *= g4.x; S[d + 1] *= g4.y; S[d + 2] *= g4.z; S[d + 3] *= g4.w;
-                rk = fmaf(S[d], k4.x, rk); rk = fmaf(S[d + 1], k4.y, rk); rk = fmaf(S[d + 2], k4.z, rk); rk = fmaf(S[d + 3], k4.w, rk);
-                rq = fmaf(S[d], q4.x, rq); rq = fmaf(S[d + 1], q4.y, rq); rq = fmaf(S[d + 2], q4.z, rq); rq = fmaf(S[d + 3], q4.w, rq);
-            }
-            const float u = beta_s[t] * (vv - rk);
-#pragma unroll
-            for (int d = 0; d < DMAX; d += 4) {
-                const float4 k4 = *reinterpret_cast<const float4*>(&k_s[t][d]);
-                S[d] = fmaf(k4.x, u, S[d]); S[d + 1] = fmaf(k4.y, u, S[d + 1]); S[d + 2] = fmaf(k4.z, u, S[d + 2]); S[d + 3] = fmaf(k4.w, u, S[d + 3]);
-            }
-            if (live) out[(size_t)n * H * DV + h * DV + col] = fmaf(u, kq_s[t], rq);
+        for (int n = 0; n < VPT; ++n) {
+            const int j = SCAN_THREADS - 1 - threadIdx.x + n * SCAN_THREADS;
+            const int t = j / COLS, c = blockIdx.x * COLS + j % COLS;
+            pre_v[n] = (j < count * COLS && c < DV) ? to_f32(v[(size_t)(base + t) * v_stride + v_col + h * DV + c]) : 0.f;
         }
+    };
+    auto store_small = [&](int buf) {
+        if (threadIdx.x < SCAN_TILE) {
+            beta_s[buf * SCAN_TILE + threadIdx.x] = pre_beta;
+            kq_s[buf * SCAN_TILE + threadIdx.x] = pre_kq;
+        }
+#pragma unroll
+        for (int n = 0; n < VPT; ++n) {
+            const int j = SCAN_THREADS - 1 - threadIdx.x + n * SCAN_THREADS;
+            if (j < SCAN_TILE * COLS) v_s[buf * SCAN_TILE * COLS + j] = pre_v[n];
+        }
+    };
+    const int my_col = threadIdx.x / PARTS;
+    if (s0 < s1) {
+        fetch(s0, 0);
+        load_small(s0);
+        store_small(0);
     }
-    if (live) {
+    cp_commit();
+    int buf = 0;
+    for (int base = s0; base < s1; base += SCAN_TILE, buf ^= 1) {
+        const int count = min(SCAN_TILE, s1 - base);
+        const bool more = base + SCAN_TILE < s1;
+        if (more) {
+            fetch(base + SCAN_TILE, buf ^ 1);
+            load_small(base + SCAN_TILE);
+        }
+        cp_commit();
+        cp_wait<1>();
+        __syncthreads();                       // this tile is in shared memory
+        const float* kb = k_s + buf * SCAN_TILE * DMAX + 4 * part;
+        const float* qb = q_s + buf * SCAN_TILE * DMAX + 4 * part;
+        const float* gb = g_s + buf * SCAN_TILE * DMAX + 4 * part;
 #pragma unroll
-        for (int d = 0; d < DMAX; ++d)
-            if (d < D) st[(size_t)d * DV] = S[d];
+        for (int t = 0; t < SCAN_TILE; ++t) {
+            if (t < count) {
+                float rk0 = 0.f, rk1 = 0.f, rq0 = 0.f, rq1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPL / 4; ++i) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kb + t * DMAX + 4 * PARTS * i);
+                    const float4 q4 = *reinterpret_cast<const float4*>(qb + t * DMAX + 4 * PARTS * i);
+                    const float4 g4 = *reinterpret_cast<const float4*>(gb + t * DMAX + 4 * PARTS * i);
+                    float* s = S + 4 * i;
+                    s[0] *= g4.x; s[1] *= g4.y; s[2] *= g4.z; s[3] *= g4.w;
+                    rk0 = fmaf(s[0], k4.x, rk0); rk1 = fmaf(s[1], k4.y, rk1); rk0 = fmaf(s[2], k4.z, rk0); rk1 = fmaf(s[3], k4.w, rk1);
+                    rq0 = fmaf(s[0], q4.x, rq0); rq1 = fmaf(s[1], q4.y, rq1); rq0 = fmaf(s[2], q4.z, rq0); rq1 = fmaf(s[3], q4.w, rq1);
+                }
+                const float rk = parts_sum<PARTS>(rk0 + rk1), rq = parts_sum<PARTS>(rq0 + rq1);
+                const float u = beta_s[buf * SCAN_TILE + t] * (v_s[(buf * SCAN_TILE + t) * COLS + my_col] - rk);
+#pragma unroll
+                for (int i = 0; i < DPL / 4; ++i) {
+                    const float4 k4 = *reinterpret_cast<const float4*>(kb + t * DMAX + 4 * PARTS * i);
+                    float* s = S + 4 * i;
+                    s[0] = fmaf(k4.x, u, s[0]); s[1] = fmaf(k4.y, u, s[1]); s[2] = fmaf(k4.z, u, s[2]); s[3] = fmaf(k4.w, u, s[3]);
+                }
+                if (live && part == 0) out[(size_t)(base + t) * H * DV + h * DV + col] = fmaf(u, kq_s[buf * SCAN_TILE + t], rq);
+            }
+        }
+        if (more) store_small(buf ^ 1);
+        __syncthreads();                       // everyone is done with this stage before it is filled again
     }
+    cp_wait<0>();
+    // Only now may the next kernel's blocks move in: they would wait for this kernel's end, and a multiprocessor full of
+    // waiting warps slowed this kernel's own long walk by a third (measured).
+    pdl_trigger();
+    if (live) store_column<DPL, PARTS>(S, st, part, D, vec);
 }
 
 // ------------------------------------------------------------------------------------------------
 // The state-space recurrence with one decay per head. Per head, S is [NS, DV]; for every token, in order:
 //   dt = softplus(dt_raw + dt_bias[h]);  S <- exp(-exp(A_log[h]) dt) S + dt B x^T;  y = S^T C + D[h] x
-// B and C belong to the head's group. A lane owns a column of S (NS entries in registers), as above.
+// B and C belong to the head's group and come straight from the convolution's result (type T), so their tiles are filled with
+// plain loads a tile ahead; step size and decay are computed while a tile is loaded.
 template <typename T, int NMAX>
-__global__ void __launch_bounds__(32) ssm_scan_kernel(const T* __restrict__ xbc, int x_stride, int x_col, int b_col, int c_col,
-                                                      const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ A_log,
-                                                      const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
-                                                      float* __restrict__ state, const int* __restrict__ seq_starts,
-                                                      const int* __restrict__ seq_slots, float* __restrict__ out, int H, int G, int NS,
-                                                      int DV) {
-    __shared__ __align__(16) float b_s[SCAN_TILE][NMAX], c_s[SCAN_TILE][NMAX];
-    __shared__ float a_s[SCAN_TILE], dt_s[SCAN_TILE];
-    pdl_trigger();
-    const int lane = threadIdx.x;
-    const int col = blockIdx.x * 32 + lane;
+__global__ void __launch_bounds__(SCAN_THREADS) ssm_scan_kernel(const T* __restrict__ xbc, int x_stride, int x_col, int b_col, int c_col,
+                                                                const T* __restrict__ dt_raw, int dt_stride, const float* __restrict__ A_log,
+                                                                const float* __restrict__ dt_bias, const float* __restrict__ Dskip,
+                                                                float* __restrict__ state, const int* __restrict__ seq_starts,
+                                                                const int* __restrict__ seq_slots, float* __restrict__ out, int H, int G,
+                                                                int NS, int DV) {
+    constexpr int PARTS = ScanParts<NMAX>::value, DPL = NMAX / PARTS, COLS = SCAN_THREADS / PARTS;
+    extern __shared__ __align__(16) float scan_smem[];
+    float* b_s = scan_smem;                              // [2][SCAN_TILE][NMAX]
+    float* c_s = b_s + 2 * SCAN_TILE * NMAX;
+    float* a_s = c_s + 2 * SCAN_TILE * NMAX;             // [2][SCAN_TILE]
+    float* dt_s = a_s + 2 * SCAN_TILE;
+    float* x_s = dt_s + 2 * SCAN_TILE;                   // [2][SCAN_TILE][COLS]
+    const int part = threadIdx.x % PARTS;
+    const int col = blockIdx.x * COLS + threadIdx.x / PARTS;
     const int h = blockIdx.y, r = blockIdx.z;
     const int g = h / (H / G);
     const bool live = col < DV;
+    const bool vec = (NS & 3) == 0;
     const float rate = expf(A_log[h]), bias = dt_bias[h], skip = Dskip[h];
     pdl_wait();
     const int s0 = seq_starts[r], s1 = seq_starts[r + 1];
-    float* st = state + (((size_t)seq_slots[r] * H + h) * NS) * DV + col;
-    float S[NMAX];
-#pragma unroll
-    for (int d = 0; d < NMAX; ++d) S[d] = (live && d < NS) ? st[(size_t)d * DV] : 0.f;
-    for (int base = s0; base < s1; base += SCAN_TILE) {
+    float* st = state + (((size_t)seq_slots[r] * H + h) * DV + (live ? col : 0)) * NS;
+    float S[DPL];
+    load_column<DPL, PARTS>(S, st, part, NS, live, vec);
+    // A tile (B and C of its tokens, step size and decay, the block's columns of x) is loaded into registers a tile ahead and
+    // put into shared memory after the tile's work, so that nobody waits for it.
+    constexpr int BPT = (SCAN_TILE * NMAX + SCAN_THREADS - 1) / SCAN_THREADS;
+    constexpr int XPT = (SCAN_TILE * COLS + SCAN_THREADS - 1) / SCAN_THREADS;
+    float pre_b[BPT], pre_c[BPT], pre_x[XPT], pre_dt = 0.f;
+    auto load_tile = [&](int base) {
         const int count = min(SCAN_TILE, s1 - base);
-        __syncwarp();
-        for (int i = lane; i < count * NMAX; i += 32) {
+#pragma unroll
+        for (int n = 0; n < BPT; ++n) {
+            const int i = threadIdx.x + n * SCAN_THREADS;
             const int t = i / NMAX, d = i % NMAX;
+            const bool in = t < count && d < NS;
             const size_t row = (size_t)(base + t) * x_stride;
-            const bool in = d < NS;
-            b_s[t][d] = in ? to_f32(xbc[row + b_col + g * NS + d]) : 0.f;
-            c_s[t][d] = in ? to_f32(xbc[row + c_col + g * NS + d]) : 0.f;
+            pre_b[n] = in ? to_f32(xbc[row + b_col + g * NS + d]) : 0.f;
+            pre_c[n] = in ? to_f32(xbc[row + c_col + g * NS + d]) : 0.f;
         }
-        if (lane < count) {
-            const float dt = softplus_f(to_f32(dt_raw[(size_t)(base + lane) * dt_stride + h]) + bias);
-            dt_s[lane] = dt;
-            a_s[lane] = expf(-rate * dt);
-        }
-        __syncwarp();
-        for (int t = 0; t < count; ++t) {
-            const int n = base + t;
-            const float x = live ? to_f32(xbc[(size_t)n * x_stride + x_col + h * DV + col]) : 0.f;
-            const float a = a_s[t], u = dt_s[t] * x;
-            float y = 0.f;
+        if (threadIdx.x < count) pre_dt = to_f32(dt_raw[(size_t)(base + threadIdx.x) * dt_stride + h]);
 #pragma unroll
-            for (int d = 0; d < NMAX; d += 4) {
-                const float4 b4 = *reinterpret_cast<const float4*>(&b_s[t][d]);
-                const float4 c4 = *reinterpret_cast<const float4*>(&c_s[t][d]);
-                S[d] = fmaf(a, S[d], b4.x * u); S[d + 1] = fmaf(a, S[d + 1], b4.y * u);
-                S[d + 2] = fmaf(a, S[d + 2], b4.z * u); S[d + 3] = fmaf(a, S[d + 3], b4.w * u);
-                y = fmaf(S[d], c4.x, y); y = fmaf(S[d + 1], c4.y, y); y = fmaf(S[d + 2], c4.z, y); y = fmaf(S[d + 3], c4.w, y);
+        for (int n = 0; n < XPT; ++n) {
+            const int j = SCAN_THREADS - 1 - threadIdx.x + n * SCAN_THREADS;
+            const int t = j / COLS, c = blockIdx.x * COLS + j % COLS;
+            pre_x[n] = (j < count * COLS && c < DV) ? to_f32(xbc[(size_t)(base + t) * x_stride + x_col + h * DV + c]) : 0.f;
+        }
+    };
+    auto store_tile = [&](int buf) {
+#pragma unroll
+        for (int n = 0; n < BPT; ++n) {
+            const int i = threadIdx.x + n * SCAN_THREADS;
+            if (i < SCAN_TILE * NMAX) {
+                b_s[buf * SCAN_TILE * NMAX + i] = pre_b[n];
+                c_s[buf * SCAN_TILE * NMAX + i] = pre_c[n];
             }
-            if (live) out[(size_t)n * H * DV + h * DV + col] = fmaf(skip, x, y);
         }
-    }
-    if (live) {
+        if (threadIdx.x < SCAN_TILE) {
+            const float dt = softplus_f(pre_dt + bias);
+            dt_s[buf * SCAN_TILE + threadIdx.x] = dt;
+            a_s[buf * SCAN_TILE + threadIdx.x] = expf(-rate * dt);
+        }
 #pragma unroll
-        for (int d = 0; d < NMAX; ++d)
-            if (d < NS) st[(size_t)d * DV] = S[d];
+        for (int n = 0; n < XPT; ++n) {
+            const int j = SCAN_THREADS - 1 - threadIdx.x + n * SCAN_THREADS;
+            if (j < SCAN_TILE * COLS) x_s[buf * SCAN_TILE * COLS + j] = pre_x[n];
+        }
+    };
+    const int my_col = threadIdx.x / PARTS;
+    if (s0 < s1) {
+        load_tile(s0);
+        store_tile(0);
     }
+    int buf = 0;
+    for (int base = s0; base < s1; base += SCAN_TILE, buf ^= 1) {
+        const int count = min(SCAN_TILE, s1 - base);
+        const bool more = base + SCAN_TILE < s1;
+        __syncthreads();                       // this tile is in shared memory; everyone is done with the other stage
+        if (more) load_tile(base + SCAN_TILE);
+        const float* bb = b_s + buf * SCAN_TILE * NMAX + 4 * part;
+        const float* cb = c_s + buf * SCAN_TILE * NMAX + 4 * part;
+#pragma unroll
+        for (int t = 0; t < SCAN_TILE; ++t) {
+            if (t < count) {
+                const float xv = x_s[(buf * SCAN_TILE + t) * COLS + my_col];
+                const float a = a_s[buf * SCAN_TILE + t], u = dt_s[buf * SCAN_TILE + t] * xv;
+                float y0 = 0.f, y1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPL / 4; ++i) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(bb + t * NMAX + 4 * PARTS * i);
+                    const float4 c4 = *reinterpret_cast<const float4*>(cb + t * NMAX + 4 * PARTS * i);
+                    float* s = S + 4 * i;
+                    s[0] = fmaf(a, s[0], b4.x * u); s[1] = fmaf(a, s[1], b4.y * u); s[2] = fmaf(a, s[2], b4.z * u); s[3] = fmaf(a, s[3], b4.w * u);
+                    y0 = fmaf(s[0], c4.x, y0); y1 = fmaf(s[1], c4.y, y1); y0 = fmaf(s[2], c4.z, y0); y1 = fmaf(s[3], c4.w, y1);
+                }
+                const float y = parts_sum<PARTS>(y0 + y1);
+                if (live && part == 0) out[(size_t)(base + t) * H * DV + h * DV + col] = fmaf(skip, xv, y);
+            }
+        }
+        if (more) store_tile(buf ^ 1);         // (the other stage: nobody reads it before the next barrier)
+    }
+    pdl_trigger();                             // (not before: see the delta rule's kernel)
+    if (live) store_column<DPL, PARTS>(S, st, part, NS, vec);
 }
 
 template <typename T>
@@ -279,10 +448,16 @@ int launch_conv(const T* z, int z_stride, int C, const float* w, const float* bi
 template <typename T>
 int launch_delta_scan(const T* v, int v_stride, int v_col, const float* qn, const float* kn, const float* kq, const float* decay,
                       const float* beta, float* state, const int* seq_starts, const int* seq_slots, float* out, int H, int G, int D,
-                      int DV, int R, cudaStream_t s) {
-    const dim3 grid((DV + 31) / 32, H, R);
-#define LLMIE_DELTA(DM) return launch_kernel(delta_scan_kernel<T, DM>, grid, dim3(32), 0, s, v, v_stride, v_col, qn, kn, kq, decay, beta, state, \
-                                             seq_starts, seq_slots, out, H, G, D, DV)
+                      int DV, int R, bool alone, cudaStream_t s) {
+#define LLMIE_DELTA(DM)                                                                                                                          \
+    {                                                                                                                                            \
+        constexpr int cols = SCAN_THREADS / ScanParts<DM>::value;                                                                                \
+        const dim3 grid((DV + cols - 1) / cols, H, R);                                                                                           \
+        const size_t smem = sizeof(float) * (2 * SCAN_TILE * (3 * DM + 2 + cols));                                                                      \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(delta_scan_kernel<T, DM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);            \
+        return launch_kernel_on(alone, delta_scan_kernel<T, DM>, grid, dim3(SCAN_THREADS), smem, s, v, v_stride, v_col, qn, kn, kq, decay, beta, \
+                                state, seq_starts, seq_slots, out, H, G, D, DV);                                                                 \
+    }
     if (D <= 16) LLMIE_DELTA(16);
     if (D <= 32) LLMIE_DELTA(32);
     if (D <= 64) LLMIE_DELTA(64);
@@ -294,10 +469,15 @@ int launch_delta_scan(const T* v, int v_stride, int v_col, const float* qn, cons
 template <typename T>
 int launch_ssm_scan(const T* xbc, int x_stride, int x_col, int b_col, int c_col, const T* dt_raw, int dt_stride, const float* A_log,
                     const float* dt_bias, const float* Dskip, float* state, const int* seq_starts, const int* seq_slots, float* out,
-                    int H, int G, int NS, int DV, int R, cudaStream_t s) {
-    const dim3 grid((DV + 31) / 32, H, R);
-#define LLMIE_SSM(NM) return launch_kernel(ssm_scan_kernel<T, NM>, grid, dim3(32), 0, s, xbc, x_stride, x_col, b_col, c_col, dt_raw, dt_stride, \
-                                           A_log, dt_bias, Dskip, state, seq_starts, seq_slots, out, H, G, NS, DV)
+                    int H, int G, int NS, int DV, int R, bool alone, cudaStream_t s) {
+#define LLMIE_SSM(NM)                                                                                                                            \
+    {                                                                                                                                            \
+        constexpr int cols = SCAN_THREADS / ScanParts<NM>::value;                                                                                \
+        const dim3 grid((DV + cols - 1) / cols, H, R);                                                                                           \
+        const size_t smem = sizeof(float) * (2 * SCAN_TILE * (2 * NM + 2 + cols));                                                                      \
+        return launch_kernel_on(alone, ssm_scan_kernel<T, NM>, grid, dim3(SCAN_THREADS), smem, s, xbc, x_stride, x_col, b_col, c_col, dt_raw,    \
+                                dt_stride, A_log, dt_bias, Dskip, state, seq_starts, seq_slots, out, H, G, NS, DV);                              \
+    }
     if (NS <= 16) LLMIE_SSM(16);
     if (NS <= 32) LLMIE_SSM(32);
     if (NS <= 64) LLMIE_SSM(64);
@@ -333,26 +513,28 @@ LLMIE_API int llmie_delta_prepare(const void* qkv, int qkv_stride, int q_col, in
                          (const bf16*)b, b_stride, A_log, dt_bias, qn, kn, kq, decay, beta, N, H, G, D, q_scale, unit_eps);
 }
 
-// state [slots][H][D][DV] float; out [N][H * DV] float
+// state [slots][H][DV][D] float (column by column); out [N][H * DV] float
 LLMIE_API int llmie_delta_scan(const void* v, int v_stride, int v_col, const float* qn, const float* kn, const float* kq,
                                const float* decay, const float* beta, float* state, const int* seq_starts, const int* seq_slots,
-                               float* out, int H, int G, int D, int DV, int R, int dtype, cudaStream_t s) {
+                               float* out, int H, int G, int D, int DV, int R, int max_rows, int dtype, cudaStream_t s) {
     if (R <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || D <= 0 || D > 256 || DV <= 0 || H > 65535 || R > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    const bool alone = max_rows >= SCAN_ALONE_ROWS;   // a long walk: see launch_kernel_on
     if (dtype == DT_F32)
-        return launch_delta_scan<float>((const float*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, s);
-    return launch_delta_scan<bf16>((const bf16*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, s);
+        return launch_delta_scan<float>((const float*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, s);
+    return launch_delta_scan<bf16>((const bf16*)v, v_stride, v_col, qn, kn, kq, decay, beta, state, seq_starts, seq_slots, out, H, G, D, DV, R, alone, s);
 }
 
-// state [slots][H][NS][DV] float; out [N][H * DV] float
+// state [slots][H][DV][NS] float (column by column); out [N][H * DV] float
 LLMIE_API int llmie_ssm_scan(const void* xbc, int x_stride, int x_col, int b_col, int c_col, const void* dt_raw, int dt_stride,
                              const float* A_log, const float* dt_bias, const float* Dskip, float* state, const int* seq_starts,
-                             const int* seq_slots, float* out, int H, int G, int NS, int DV, int R, int dtype, cudaStream_t s) {
+                             const int* seq_slots, float* out, int H, int G, int NS, int DV, int R, int max_rows, int dtype, cudaStream_t s) {
     if (R <= 0) return 0;
     if (H <= 0 || G <= 0 || H % G || NS <= 0 || NS > 256 || DV <= 0 || H > 65535 || R > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    const bool alone = max_rows >= SCAN_ALONE_ROWS;
     if (dtype == DT_F32)
         return launch_ssm_scan<float>((const float*)xbc, x_stride, x_col, b_col, c_col, (const float*)dt_raw, dt_stride, A_log, dt_bias, Dskip,
-                                      state, seq_starts, seq_slots, out, H, G, NS, DV, R, s);
+                                      state, seq_starts, seq_slots, out, H, G, NS, DV, R, alone, s);
     return launch_ssm_scan<bf16>((const bf16*)xbc, x_stride, x_col, b_col, c_col, (const bf16*)dt_raw, dt_stride, A_log, dt_bias, Dskip, state,
-                                 seq_starts, seq_slots, out, H, G, NS, DV, R, s);
+                                 seq_starts, seq_slots, out, H, G, NS, DV, R, alone, s);
 }

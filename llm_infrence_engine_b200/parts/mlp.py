@@ -64,8 +64,8 @@ class DenseMLP(FeedForward):
 
 class ClampedGLU(FeedForward):
     """``down(g * sigmoid(alpha g) * (u + shift))`` with ``g = min(gate(x), limit)`` and ``u = clamp(up(x), -limit, limit)``, no
-    biases. ``gate`` and ``up`` are one matrix ``[2 * intermediate, hidden]`` (gate rows first); the gated unit is computed in
-    32-bit on the product's sums where those are at hand (small batches)."""
+    biases. ``gate`` and ``up`` are one matrix ``[2 * intermediate, hidden]`` (gate rows first); the gated unit is the epilogue of
+    that product (prompt portions) or one kernel over its float32 sums (decode steps): ``gate_up_act`` of the kernels object decides."""
 
     graph_safe = True
 
@@ -86,5 +86,4 @@ class ClampedGLU(FeedForward):
 
     def forward(self, ctx, h, residual):
         K = ctx.K
-        y = K.glu_clamped(K.linear(h, self.w_gate_up, transient=True), self.limit, self.alpha, self.shift, ctx.dtype)
-        K.linear(y, self.w_down, add_to=residual)
+        K.linear(K.gate_up_act(h, self.w_gate_up, ctx.dtype, glu=(self.limit, self.alpha, self.shift)), self.w_down, add_to=residual)

@@ -45,8 +45,7 @@ class GatedDeltaMixer(Mixer):
         self.conv_taps, self.eps, self.prefix, self.random_rank = int(conv_taps), float(eps), prefix, random_rank
         self.qk = num_kv_heads * head_dim
         self.channels = 2 * self.qk + num_heads * v_head_dim      # what the convolution sees: q | k | v
-        self.b_col = self.channels
-        self.a1_col = self.b_col + num_heads
+        self.b_col = self.a1_col = self.g1_col = 0      # columns of the joined projection's sections: set when the weights are bound
         self.w_in = self.w_a2 = self.w_g2 = self.w_o = self.conv_w = self.A_log = self.dt_bias = self.norm_w = None
 
     def params(self) -> Dict[str, ParamSpec]:
@@ -69,13 +68,21 @@ class GatedDeltaMixer(Mixer):
     def bind(self, tensors) -> None:
         super().bind(tensors)
         self.rank_a, self.rank_g = self.w_a2.shape[1], self.w_g2.shape[1]
-        if self.w_in.shape[0] != self.a1_col + self.rank_a + self.rank_g:
+        rows = (self.channels, self.num_heads, self.rank_a, self.rank_g)
+        if self.w_in.shape[0] != sum(rows):
             raise ValueError(f"{self.prefix}: the two halves of a low-rank projection do not agree on its rank")
-        self.g1_col = self.a1_col + self.rank_a
-        self.w_in = _padded(self.w_in)
+        # every section of the joined projection starts on a multiple of 8 rows: its columns of the product then start on a
+        # 16-byte boundary, and the second halves of the low-rank projections can read them where they lie
+        pieces, starts, at = [], [], 0
+        for part in torch.split(self.w_in, rows):
+            starts.append(at)
+            pieces.append(_padded(part))
+            at += pieces[-1].shape[0]
+        _, self.b_col, self.a1_col, self.g1_col = starts
+        self.w_in = torch.cat(pieces).contiguous()
 
     def cache_spec(self):
-        return (FixedStateSpec((self.num_heads, self.head_dim, self.v_head_dim)), FixedStateSpec((self.conv_taps - 1, self.channels)))
+        return (FixedStateSpec((self.num_heads, self.v_head_dim, self.head_dim)), FixedStateSpec((self.conv_taps - 1, self.channels)))   # S column by column
 
     def forward(self, ctx, h, cache, residual):
         K = ctx.K
@@ -83,8 +90,8 @@ class GatedDeltaMixer(Mixer):
         H, G, D, DV = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
         z = K.linear(h, self.w_in, out_dtype=ctx.dtype)
         qkv = K.causal_conv(z, 0, self.channels, self.conv_w, None, conv_state.state, ctx, activation="silu")
-        a = K.linear(z[:, self.a1_col:self.a1_col + self.rank_a].contiguous(), self.w_a2, out_dtype=ctx.dtype)
-        g = K.linear(z[:, self.g1_col:self.g1_col + self.rank_g].contiguous(), self.w_g2, out_dtype=ctx.dtype)
+        a = K.linear(z[:, self.a1_col:self.a1_col + self.rank_a], self.w_a2, out_dtype=ctx.dtype)
+        g = K.linear(z[:, self.g1_col:self.g1_col + self.rank_g], self.w_g2, out_dtype=ctx.dtype)
         o = K.delta_rule(qkv, H, G, D, DV, a, z, self.b_col, self.A_log, self.dt_bias, state.state, ctx)
         y = K.group_rmsnorm_gate(o, g, 0, self.norm_w, DV, self.eps, gate_first=False, out_dtype=ctx.dtype)
         K.linear(y, self.w_o, add_to=residual)
@@ -141,7 +148,7 @@ class StateSpaceMixer(Mixer):
         self.w_in = _padded(self.w_in)
 
     def cache_spec(self):
-        return (FixedStateSpec((self.num_heads, self.state_size, self.v_head_dim)), FixedStateSpec((self.conv_taps - 1, self.channels)))
+        return (FixedStateSpec((self.num_heads, self.v_head_dim, self.state_size)), FixedStateSpec((self.conv_taps - 1, self.channels)))   # S column by column
 
     def forward(self, ctx, h, cache, residual):
         K = ctx.K

@@ -119,6 +119,19 @@ def test_group_norm_with_gate_mix_of_two_and_gated_unit(K, dtype):
         got = K.glu_clamped(K.linear(x.cuda(), w.cuda(), transient=True), 1.0, 1.702, 1.0, T)
         close(got, ref.glu_clamped(x.float() @ w.float().T, 1.0, 1.702, 1.0, T), dtype, "glu_clamped on a product's sums")
         assert float(K._acc.abs().max()) == 0.0
+        # prompt portions: the unit is the epilogue of the tcgen05 gate/up product (one block per tile, and pairs of blocks from 1,024 rows on)
+        for M, I, Kd in ((130, 40, 64), (300, 264, 96), (1100, 520, 128), (2048, 96, 256)):
+            x, w = rnd(M, Kd, seed=12).to(T), rnd(2 * I, Kd, seed=13, scale=0.3).to(T)
+            got = K.gate_up_act(x.cuda(), w.cuda(), T, glu=(1.25, 1.702, 1.0))
+            close(got, ref.gate_up_act(x, w, T, glu=(1.25, 1.702, 1.0)), dtype, f"clamped unit as the product's epilogue, {M} rows")
+        K.check_device_errors()
+        # the second half of a low-rank projection reads its input where it lies, as a run of columns of wider rows
+        z, w2 = rnd(200, 64, seed=14).to(T), rnd(48, 24, seed=15).to(T)
+        close(K.linear(z.cuda()[:, 16:40], w2.cuda(), out_dtype=T), z[:, 16:40].float() @ w2.float().T, dtype, "linear on a run of columns")
+        close(K.linear(z.cuda()[:3, 16:40], w2.cuda(), out_dtype=T), z[:3, 16:40].float() @ w2.float().T, dtype, "linear on a run of columns, few rows")
+    else:
+        z, w2 = rnd(20, 64, seed=14), rnd(48, 24, seed=15)
+        close(K.linear(z.cuda()[:, 16:40], w2.cuda()), z[:, 16:40] @ w2.T, dtype, "linear on a run of columns", f32=4e-6)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -173,7 +186,7 @@ def test_short_convolution_over_ragged_steps(K, dtype, C, taps, bias, act):
 @pytest.mark.parametrize("H,G,D,DV", [(4, 2, 16, 24), (3, 3, 8, 40), (6, 2, 40, 33), (2, 1, 128, 128), (2, 2, 64, 32), (1, 1, 200, 16)])
 def test_delta_rule_over_ragged_steps(K, dtype, H, G, D, DV):
     ref, T = TorchKernels(), TD[dtype]
-    state = torch.zeros(4, H, D, DV)
+    state = torch.zeros(4, H, DV, D)
     dstate = state.clone().cuda()
     A_log, dt_bias = torch.log(0.5 + rnd(H, seed=1).abs()), rnd(H * D, seed=2) - 2.0
     for step, lens in enumerate(([37, 1, 5], [1, 1, 1], [2, 19, 1])):
@@ -191,7 +204,7 @@ def test_delta_rule_over_ragged_steps(K, dtype, H, G, D, DV):
 @pytest.mark.parametrize("H,G,NS,DV", [(4, 1, 16, 12), (6, 2, 8, 16), (2, 2, 40, 20), (8, 1, 128, 64), (3, 3, 64, 33)])
 def test_state_space_scan_over_ragged_steps(K, dtype, H, G, NS, DV):
     ref, T = TorchKernels(), TD[dtype]
-    state = torch.zeros(4, H, NS, DV)
+    state = torch.zeros(4, H, DV, NS)
     dstate = state.clone().cuda()
     A_log, dt_bias, skip = torch.log(0.5 + rnd(H, seed=1).abs()), rnd(H, seed=2) - 1.0, 1 + rnd(H, seed=3, scale=0.2)
     for step, lens in enumerate(([41, 1, 3], [1, 1, 1], [2, 23, 1])):

@@ -119,8 +119,8 @@ def test_builder_names_the_checkpoint_tensors_and_the_cache():
     assert [(c.layer, c.cache, c.write) for c in spec.schedule] == [(0, 0, True), (1, 1, True), (2, 2, True), (1, 3, True), (0, 4, True), (2, 5, True)]
     specs = spec.cache_specs()
     assert specs[1] == PagedKVSpec(2, 24, 19, 16, 3, None) == specs[3]
-    assert specs[0] == (FixedStateSpec((4, 16, 24)), FixedStateSpec((2, 2 * 2 * 16 + 4 * 24)))
-    assert specs[2] == ((PagedKVSpec(1, 32, None, 32, 0, 21), FixedStateSpec((1, 4 * 32 + 32 + 32))), (FixedStateSpec((4, 16, 12)), FixedStateSpec((3, 48 + 32))))
+    assert specs[0] == (FixedStateSpec((4, 24, 16)), FixedStateSpec((2, 2 * 2 * 16 + 4 * 24)))
+    assert specs[2] == ((PagedKVSpec(1, 32, None, 32, 0, 21), FixedStateSpec((1, 4 * 32 + 32 + 32))), (FixedStateSpec((4, 12, 16)), FixedStateSpec((3, 48 + 32))))
     groups, of_entry = group_layout(specs)
     assert len(groups) == 2 and of_entry == [(None, None), 0, ((1, None), (None, None)), 0, (None, None), ((1, None), (None, None))]
     assert has_fixed_state(specs)
@@ -144,6 +144,7 @@ def test_weights_load_and_the_low_ranks_come_from_the_checkpoint(tmp_path):
     mixer = spec.layers[1].mixer
     assert (mixer.rank_a, mixer.rank_g) == (5, 11) and mixer.w_in.shape[0] % 8 == 0
     assert torch.equal(mixer.w_in[mixer.a1_col:mixer.a1_col + 5], t["l1.mix.a1"]) and torch.equal(mixer.w_in[mixer.g1_col:mixer.g1_col + 11], t["l1.mix.g1"])
+    assert torch.equal(mixer.w_in[mixer.b_col:mixer.b_col + 6], t["l1.mix.b"]) and mixer.b_col % 8 == 0 and mixer.a1_col % 8 == 0 and mixer.g1_col % 8 == 0
     assert spec.head.matrix() is spec.embedding.table and spec.embedding.scale == 0.5
     assert spec.layers[0].mixer.conv_taps == 0 and spec.layers[2].mixer.left.conv_w.shape == ((6 + 3) * 16 + 3 * 16, 3)
 

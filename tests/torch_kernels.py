@@ -112,7 +112,9 @@ class TorchKernels:
                 out[t, h] = pr @ v[:, h // rep]
         return out.reshape(N, num_heads * d).to(qkv.dtype)
 
-    def gate_up_act(self, x, w_gate_up, out_dtype=None):
+    def gate_up_act(self, x, w_gate_up, out_dtype=None, glu=None):
+        if glu is not None:
+            return self.glu_clamped(self.linear(x, w_gate_up, out_dtype=torch.float32), *glu, out_dtype or x.dtype)
         return self.silu_mul(self.linear(x, w_gate_up, out_dtype=torch.float32)).to(out_dtype or x.dtype)
 
     def silu_mul(self, gu, out_dtype=None):
@@ -300,13 +302,13 @@ class TorchKernels:
         for slot, s0, s1 in self._requests(batch):
             for h in range(H):
                 g = h // (H // G)
-                S = state[slot, h].clone()
+                S = state[slot, h].T.clone()          # the state is kept column by column: [v_head_dim, head_dim]
                 for n in range(s0, s1):
                     S = decay[n, h][:, None] * S
                     u = beta[n, h] * (v[n, h] - S.T @ k[n, g])
                     S = S + torch.outer(k[n, g], u)
                     out[n, h] = S.T @ q[n, g]
-                state[slot, h] = S
+                state[slot, h] = S.T
         return out.reshape(N, H * DV)
 
     def ssm_scan(self, xbc, num_heads, groups, state_size, v_head_dim, dt, dt_col, A_log, dt_bias, skip, state, batch):
@@ -320,11 +322,11 @@ class TorchKernels:
         for slot, s0, s1 in self._requests(batch):
             for h in range(H):
                 g = h // (H // G)
-                S = state[slot, h].clone()
+                S = state[slot, h].T.clone()          # kept column by column: [v_head_dim, state_size]
                 for n in range(s0, s1):
                     S = decay[n, h] * S + step[n, h] * torch.outer(B[n, g], x[n, h])
                     out[n, h] = S.T @ C[n, g] + skip[h] * x[n, h]
-                state[slot, h] = S
+                state[slot, h] = S.T
         return out.reshape(N, H * DV)
 
     # ------------------------------------------------------------------ latent attention
