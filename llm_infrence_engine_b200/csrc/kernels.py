@@ -784,7 +784,8 @@ class CudaKernels:
         if buf is None or buf.numel() < N * H or buf.device != streams.device:
             if buf is not None:
                 self._retired_acc.append(buf)   # a captured graph may still add into it and clear it
-            buf = self._zero_bufs[index] = torch.zeros(max(N * H, 1 << 20), dtype=torch.float32, device=streams.device)
+            with torch.inference_mode(False):   # an ordinary tensor: it is also cleared from code that runs outside inference mode
+                buf = self._zero_bufs[index] = torch.zeros(max(N * H, 1 << 20), dtype=torch.float32, device=streams.device)
         out = buf[: N * H].view(N, H)
         self._fresh = [t for t in self._fresh if t.untyped_storage().data_ptr() != buf.untyped_storage().data_ptr()] + [out]
         return out

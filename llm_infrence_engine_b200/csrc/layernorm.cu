@@ -20,14 +20,20 @@ __device__ __forceinline__ float sigmoid_f(float x) { return 1.0f / (1.0f + expf
 template <int VEC>
 __device__ __forceinline__ void row_stats(const float* buf, int H, int step, float eps, float* scratch, float& mean, float& rstd) {
     float sum = 0.f;
-    for (int i = threadIdx.x * VEC; i < H; i += step)
+    for (int i = threadIdx.x * VEC; i < H; i += step) {
+        float v[VEC];
+        if constexpr (VEC == 4) load4(buf + i, v); else v[0] = buf[i];   // (16-byte accesses: four floats apart, the threads would collide on the banks)
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) sum += buf[i + j];
+        for (int j = 0; j < VEC; ++j) sum += v[j];
+    }
     mean = block_sum(sum, scratch) / (float)H;
     float sq = 0.f;
-    for (int i = threadIdx.x * VEC; i < H; i += step)
+    for (int i = threadIdx.x * VEC; i < H; i += step) {
+        float v[VEC];
+        if constexpr (VEC == 4) load4(buf + i, v); else v[0] = buf[i];
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) { const float d = buf[i + j] - mean; sq = fmaf(d, d, sq); }
+        for (int j = 0; j < VEC; ++j) { const float d = v[j] - mean; sq = fmaf(d, d, sq); }
+    }
     rstd = 1.0f / sqrtf(block_sum(sq, scratch) / (float)H + eps);
 }
 
@@ -61,8 +67,7 @@ __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, cons
         float v[VEC], u[VEC];
         if constexpr (VEC == 4) load4(xr + i, v); else v[0] = xr[i];
         if (yr) { if constexpr (VEC == 4) load4(yr + i, u); else u[0] = to_f32(yr[i]); }
-#pragma unroll
-        for (int j = 0; j < VEC; ++j) { x_buf[i + j] = v[j]; if (yr) y_buf[i + j] = u[j]; }
+        if constexpr (VEC == 4) { store4(x_buf + i, v); if (yr) store4(y_buf + i, u); } else { x_buf[i] = v[0]; if (yr) y_buf[i] = u[0]; }
         if (yr && clear_y) {
             const float zero[4] = {0.f, 0.f, 0.f, 0.f};
             if constexpr (VEC == 4) store4(yr + i, zero); else yr[i] = from_f32<TY>(0.f);
@@ -72,9 +77,11 @@ __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, cons
         float mean, rstd;
         row_stats<VEC>(y_buf, H, step, eps, scratch, mean, rstd);
         for (int i = threadIdx.x * VEC; i < H; i += step) {
-            float v[VEC];
+            float v[VEC], u[VEC], w[VEC];
+            if constexpr (VEC == 4) { load4(x_buf + i, v); load4(y_buf + i, u); load4(wp_buf + i, w); } else { v[0] = x_buf[i]; u[0] = y_buf[i]; w[0] = wp_buf[i]; }
 #pragma unroll
-            for (int j = 0; j < VEC; ++j) { v[j] = x_buf[i + j] + (y_buf[i + j] - mean) * rstd * wp_buf[i + j]; x_buf[i + j] = v[j]; }
+            for (int j = 0; j < VEC; ++j) v[j] += (u[j] - mean) * rstd * w[j];
+            if constexpr (VEC == 4) store4(x_buf + i, v); else x_buf[i] = v[0];
             if (!rows) { if constexpr (VEC == 4) store4(xr + i, v); else xr[i] = v[0]; }
         }
     }
@@ -83,9 +90,10 @@ __global__ void layernorm_kernel(float* __restrict__ x, TY* __restrict__ y, cons
     row_stats<VEC>(x_buf, H, step, eps, scratch, mean, rstd);
     TO* o = out + (size_t)blockIdx.x * H;
     for (int i = threadIdx.x * VEC; i < H; i += step) {
-        float v[VEC];
+        float v[VEC], w[VEC];
+        if constexpr (VEC == 4) { load4(x_buf + i, v); load4(wq_buf + i, w); } else { v[0] = x_buf[i]; w[0] = wq_buf[i]; }
 #pragma unroll
-        for (int j = 0; j < VEC; ++j) v[j] = (x_buf[i + j] - mean) * rstd * wq_buf[i + j];
+        for (int j = 0; j < VEC; ++j) v[j] = (v[j] - mean) * rstd * w[j];
         if constexpr (VEC == 4) store4(o + i, v); else o[i] = from_f32<TO>(v[0]);
     }
 }
