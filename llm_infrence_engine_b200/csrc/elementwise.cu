@@ -67,6 +67,26 @@ LLMIE_API int llmie_zero_fresh_state(float* state, long long row_floats, const i
     return launch_kernel(zero_fresh_state_kernel, dim3(num_seqs), dim3(128), 0, s, state, row_floats, slots, starts, positions);
 }
 
+// The same for several state tensors in one launch: grid = (requests, tensors); states[i] is tensor i's address, row_floats[i]
+// the floats of one of its rows.
+__global__ void zero_fresh_states_kernel(const long long* __restrict__ states, const long long* __restrict__ row_floats,
+                                         const int* __restrict__ slots, const int* __restrict__ starts, const int* __restrict__ positions) {
+    pdl_trigger();
+    pdl_wait();
+    const int r = blockIdx.x;
+    if (positions[starts[r]] != 0) return;
+    const long long n = row_floats[blockIdx.y];
+    float* row = reinterpret_cast<float*>(states[blockIdx.y]) + (long long)slots[r] * n;
+    for (long long i = threadIdx.x; i < n; i += blockDim.x) row[i] = 0.f;
+}
+
+LLMIE_API int llmie_zero_fresh_states(const long long* states, const long long* row_floats, int count, const int* slots, const int* starts,
+                                      const int* positions, int num_seqs, cudaStream_t s) {
+    if (num_seqs <= 0 || count <= 0) return 0;
+    if (count > 65535) return LLMIE_ERR_BAD_ARGUMENT;
+    return launch_kernel(zero_fresh_states_kernel, dim3(num_seqs, count), dim3(256), 0, s, states, row_floats, slots, starts, positions);
+}
+
 // ------------------------------------------------------------------------------------------------
 // cos/sin[n, j] of the angle float(position[n]) * inv_freq[j], each times `mult`, all in 32-bit
 __global__ void rope_tables_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq, float* __restrict__ cos_out,

@@ -82,6 +82,7 @@ class CudaKernels:
         # A sublayer's result whose layer norm is to be added into the residual stream waits here for the norm of the next
         # sublayer, which adds and normalises in one pass: (stream, result, the post-norm's weight, eps)
         self._pending_post: Optional[tuple] = None
+        self._state_lists: dict = {}   # the addresses of a runner's state tensors on the device (zero_fresh_states)
         self._fresh: list = []   # zeroed tensors of ``zeros_like_rows`` that nothing has been added into yet
         # ``zeros_like_rows`` hands out views of one float32 buffer that is zero between uses: the stream kernels that read a
         # sublayer's result out of it set it back to zero on their way (no fill kernel per sublayer)
@@ -103,7 +104,7 @@ class CudaKernels:
                    "llmie_kv_store", "llmie_act", "llmie_paged_attention_ext_f32", "llmie_paged_attention_ext_bf16", "llmie_paged_attention_ext_mma",
                    "llmie_attention_ext_mma_fits", "llmie_paged_attention_ext_fa", "llmie_attention_ext_fa_fits",
                    "llmie_layernorm", "llmie_group_rmsnorm_gate", "llmie_dual_rmsnorm_mix", "llmie_glu_clamped", "llmie_qk_norm_rope_store",
-                   "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan"):
+                   "llmie_causal_conv", "llmie_delta_prepare", "llmie_delta_scan", "llmie_ssm_scan", "llmie_zero_fresh_states"):
             getattr(self.lib, fn).restype = ctypes.c_int
         # two forms of the gate/up kernel live in source files of their own, and the library also builds without them
         self._gate_up_cluster = self._gate_up_pair = self._gate_up_glu_pair = None
@@ -204,6 +205,28 @@ class CudaKernels:
         if R and state.dim() >= 1 and state.shape[0]:
             self._check(self.lib.llmie_zero_fresh_state(_ptr(state), ctypes.c_longlong(state.numel() // state.shape[0]), _ptr(seq_slots),
                                                         _ptr(seq_starts), _ptr(positions), R, self._stream()), "zero_fresh_state")
+
+    def zero_fresh_states(self, states, seq_slots, seq_starts, positions):
+        """``zero_fresh_state`` for a list of state tensors in one launch (their addresses are put on the device once)."""
+        if not states:
+            return
+        if len(states) == 1:
+            return self.zero_fresh_state(states[0], seq_slots, seq_starts, positions)
+        key = tuple(t.data_ptr() for t in states)
+        if key not in self._state_lists:
+            for t in states:
+                self._need(t, "state", torch.float32)
+            with torch.inference_mode(False):
+                ptrs = torch.tensor(key, dtype=torch.int64, device=states[0].device)
+                sizes = torch.tensor([t.numel() // t.shape[0] for t in states], dtype=torch.int64, device=states[0].device)
+            self._state_lists[key] = (ptrs, sizes)   # (kept for good: a captured step holds their addresses)
+        ptrs, sizes = self._state_lists[key]
+        for name, t in (("seq_slots", seq_slots), ("seq_starts", seq_starts), ("positions", positions)):
+            self._need(t, name, torch.int32, 1)
+        R = seq_slots.shape[0]
+        if R:
+            self._check(self.lib.llmie_zero_fresh_states(_ptr(ptrs), _ptr(sizes), len(states), _ptr(seq_slots),
+                                                         _ptr(seq_starts), _ptr(positions), R, self._stream()), "zero_fresh_states")
 
     def rope_tables(self, positions, inv_freq, mult: float = 1.0):
         self._need(positions, "positions", torch.int32, 1)
@@ -1187,11 +1210,12 @@ class CudaKernels:
         ``qkv = [q: kv_heads x head_dim | k: the same | v: heads x v_head_dim]`` (after convolution and activation), ``a [N, heads * head_dim]``
         the decay's logits, ``b`` (columns from ``b_col``) the logits of beta. Returns float32 ``[N, heads * v_head_dim]``."""
         self._need(qkv, "qkv", None, 2)
-        self._need(a, "a", qkv.dtype, 2)
         self._need(state, "state", torch.float32, 4)
         N = qkv.shape[0]
         H, G, D, DV = num_heads, num_kv_heads, head_dim, v_head_dim
-        if qkv.shape[1] < 2 * G * D + H * DV or a.shape[1] != H * D or H % G or D > 256:
+        if a.dim() != 2 or a.stride(1) != 1 or a.dtype != qkv.dtype or a.shape != (N, H * D) or not a.is_cuda:
+            raise KernelError("delta_rule: the decay's logits must be [rows, heads * head_dim] of the same type (they may be columns of wider rows)")
+        if qkv.shape[1] < 2 * G * D + H * DV or H % G or D > 256:
             raise KernelError("delta_rule: the rows do not fit the head sizes (head_dim at most 256)")
         if b.dim() != 2 or b.stride(1) != 1 or b.dtype != qkv.dtype or b_col + H > b.shape[1]:
             raise KernelError("delta_rule: the beta logits must be columns of rows of the same type")
@@ -1209,7 +1233,7 @@ class CudaKernels:
             o += n
         qn, kn, decay, kq, beta = pieces
         dt = self._dt(qkv, "qkv")
-        self._check(self.lib.llmie_delta_prepare(_ptr(qkv), qkv.shape[1], 0, G * D, _ptr(a), a.shape[1], ctypes.c_void_p(b.data_ptr() + b_col * b.element_size()),
+        self._check(self.lib.llmie_delta_prepare(_ptr(qkv), qkv.shape[1], 0, G * D, _ptr(a), a.stride(0), ctypes.c_void_p(b.data_ptr() + b_col * b.element_size()),
                                                  b.stride(0), _ptr(A_log), _ptr(dt_bias), _ptr(qn), _ptr(kn), _ptr(kq), _ptr(decay), _ptr(beta), N, H, G, D,
                                                  ctypes.c_float(D ** -0.5), ctypes.c_float(unit_eps), dt, self._stream()), "delta_rule (prepare)")
         out = torch.empty((N, H * DV), dtype=torch.float32, device=dev)

@@ -391,8 +391,12 @@ class ModelRunner:
 
     def _forward(self, ctx: StepContext, logit_rows: torch.Tensor) -> Optional[torch.Tensor]:
         spec = self.spec
-        for b in self.state_bindings:   # a request's fixed-size state starts from zero: decided on the device, so captured steps do it too
-            self.K.zero_fresh_state(b.state, ctx.seq_slots, ctx.seq_starts_dev, ctx.positions)
+        # a request's fixed-size state starts from zero: decided on the device, so captured steps do it too
+        if len(self.state_bindings) > 1 and hasattr(self.K, "zero_fresh_states"):
+            self.K.zero_fresh_states([b.state for b in self.state_bindings], ctx.seq_slots, ctx.seq_starts_dev, ctx.positions)
+        else:
+            for b in self.state_bindings:
+                self.K.zero_fresh_state(b.state, ctx.seq_slots, ctx.seq_starts_dev, ctx.positions)
         residual = spec.embedding.forward(ctx)
         if spec.streams is not None:   # several residual streams: the layers work on [N, streams, hidden]
             residual = spec.streams.expand(ctx, residual)

@@ -46,7 +46,7 @@ class GatedDeltaMixer(Mixer):
         self.qk = num_kv_heads * head_dim
         self.channels = 2 * self.qk + num_heads * v_head_dim      # what the convolution sees: q | k | v
         self.b_col = self.a1_col = self.g1_col = 0      # columns of the joined projection's sections: set when the weights are bound
-        self.w_in = self.w_a2 = self.w_g2 = self.w_o = self.conv_w = self.A_log = self.dt_bias = self.norm_w = None
+        self.w_in = self.w_a2 = self.w_g2 = self.w_low2 = self.w_o = self.conv_w = self.A_log = self.dt_bias = self.norm_w = None
 
     def params(self) -> Dict[str, ParamSpec]:
         p, h, H, D, DV = self.prefix, self.hidden, self.num_heads, self.head_dim, self.v_head_dim
@@ -65,6 +65,10 @@ class GatedDeltaMixer(Mixer):
             "norm_w": ParamSpec((Source(f"{p}.norm", (DV,), INIT_NORM),), VECTOR),
         }
 
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_low2, self.w_o, self.conv_w, self.A_log, self.dt_bias, self.norm_w)
+                   if t is not None)
+
     def bind(self, tensors) -> None:
         super().bind(tensors)
         self.rank_a, self.rank_g = self.w_a2.shape[1], self.w_g2.shape[1]
@@ -80,6 +84,14 @@ class GatedDeltaMixer(Mixer):
             at += pieces[-1].shape[0]
         _, self.b_col, self.a1_col, self.g1_col = starts
         self.w_in = torch.cat(pieces).contiguous()
+        # the second halves of the two low-rank projections as ONE product: [a2 0; 0 g2] over the columns of both first halves
+        HD, HV = self.num_heads * self.head_dim, self.num_heads * self.v_head_dim
+        self.low_cols = at - self.a1_col
+        w2 = self.w_a2.new_zeros((HD + HV, self.low_cols))
+        w2[:HD, :self.rank_a] = self.w_a2
+        w2[HD:, self.g1_col - self.a1_col:self.g1_col - self.a1_col + self.rank_g] = self.w_g2
+        self.w_low2 = w2.contiguous()
+        self.w_a2 = self.w_g2 = None
 
     def cache_spec(self):
         return (FixedStateSpec((self.num_heads, self.v_head_dim, self.head_dim)), FixedStateSpec((self.conv_taps - 1, self.channels)))   # S column by column
@@ -90,10 +102,9 @@ class GatedDeltaMixer(Mixer):
         H, G, D, DV = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
         z = K.linear(h, self.w_in, out_dtype=ctx.dtype)
         qkv = K.causal_conv(z, 0, self.channels, self.conv_w, None, conv_state.state, ctx, activation="silu")
-        a = K.linear(z[:, self.a1_col:self.a1_col + self.rank_a], self.w_a2, out_dtype=ctx.dtype)
-        g = K.linear(z[:, self.g1_col:self.g1_col + self.rank_g], self.w_g2, out_dtype=ctx.dtype)
-        o = K.delta_rule(qkv, H, G, D, DV, a, z, self.b_col, self.A_log, self.dt_bias, state.state, ctx)
-        y = K.group_rmsnorm_gate(o, g, 0, self.norm_w, DV, self.eps, gate_first=False, out_dtype=ctx.dtype)
+        ag = K.linear(z[:, self.a1_col:self.a1_col + self.low_cols], self.w_low2, out_dtype=ctx.dtype)    # [decay logits | gate logits]
+        o = K.delta_rule(qkv, H, G, D, DV, ag[:, :H * D], z, self.b_col, self.A_log, self.dt_bias, state.state, ctx)
+        y = K.group_rmsnorm_gate(o, ag, H * D, self.norm_w, DV, self.eps, gate_first=False, out_dtype=ctx.dtype)
         K.linear(y, self.w_o, add_to=residual)
 
 

@@ -27,6 +27,10 @@ class TorchKernels:
         take = source_rows >= 0
         token_ids[take] = previous_tokens[source_rows[take].long()]
 
+    def zero_fresh_states(self, states, seq_slots, seq_starts, positions):
+        for state in states:
+            self.zero_fresh_state(state, seq_slots, seq_starts, positions)
+
     def zero_fresh_state(self, state, seq_slots, seq_starts, positions):
         fresh = positions[seq_starts[: seq_slots.shape[0]].long()] == 0
         state[seq_slots[fresh].long()] = 0
