@@ -408,8 +408,8 @@ class MaskedAttentionConfig:
         if cap is not None and not cap > 0:
             raise ConfigError(f"config.json: {where}'softcap' must be positive, got {cap}")
         conv = _pos_int(m, "conv", where) if m.get("conv") is not None else 0
-        if conv and not 2 <= conv <= 8:
-            raise ConfigError(f"config.json: {where}'conv' must be 2 to 8 taps, got {conv}")
+        if conv > 8:
+            raise ConfigError(f"config.json: {where}'conv' must be 1 to 8 taps, got {conv}")
         if side_by_side and not conv:
             raise ConfigError(f"config.json: {where}'conv' is missing")
         return cls(heads, kv_heads, dim, _pos_int(m, "vdim", where) if "vdim" in m else dim, _number(m, "scale", where), rot, size, keep,
@@ -434,8 +434,8 @@ class DeltaConfig:
         dim, conv = _pos_int(m, "dim", where), _pos_int(m, "conv", where)
         if dim > 256:
             raise ConfigError(f"config.json: {where}'dim' {dim}: the delta rule is built for key sizes up to 256")
-        if not 2 <= conv <= 8:
-            raise ConfigError(f"config.json: {where}'conv' must be 2 to 8 taps, got {conv}")
+        if conv > 8:
+            raise ConfigError(f"config.json: {where}'conv' must be 1 to 8 taps, got {conv}")
         return cls(heads, kv_heads, dim, _pos_int(m, "vdim", where), conv)
 
 
@@ -460,8 +460,8 @@ class StateSpaceConfig:
             raise ConfigError(f"config.json: {where}{c.heads * c.vdim} channels cannot be normed in {c.norm_groups} equal parts")
         if c.state > 256:
             raise ConfigError(f"config.json: {where}'state' {c.state}: the recurrence is built for state sizes up to 256")
-        if not 2 <= c.conv <= 8:
-            raise ConfigError(f"config.json: {where}'conv' must be 2 to 8 taps, got {c.conv}")
+        if c.conv > 8:
+            raise ConfigError(f"config.json: {where}'conv' must be 1 to 8 taps, got {c.conv}")
         return c
 
 
@@ -545,8 +545,8 @@ class ZepalornConfig:
             src = layer.weights_of
             if src is None:
                 continue
-            if src >= i or self.layers[src].weights_of is not None:
-                raise ConfigError(f"layers[{i}].weights_of {src} must name an earlier layer with tensors of its own")
+            if src == i or src >= len(self.layers) or self.layers[src].weights_of is not None:
+                raise ConfigError(f"layers[{i}].weights_of {src} must name another layer, one with tensors of its own")
             o = self.layers[src]
             if (o.kind, o.mixer, o.ff, o.ff_limit) != (layer.kind, layer.mixer, layer.ff, layer.ff_limit):
                 raise ConfigError(f"layers[{i}] runs on the weights of layer {src}, but the rest of its entry differs from that layer's")

@@ -40,10 +40,9 @@ def build_zepalorn(cfg: ZepalornConfig) -> ModelSpec:
                                window=None if m.chunked else m.mask_size, keep_first=m.keep_first, chunk=m.mask_size if m.chunked else None,
                                softcap=m.softcap, conv_taps=m.conv, qk_norm=m.qk_norm, eps=eps)
 
-    layers, schedule, part_of = [], [], {}
+    layers, part_of = [], {}
     for i, lc in enumerate(cfg.layers):
-        if lc.weights_of is not None:      # the same part once more, with cache entry i
-            schedule.append(LayerCall(part_of[lc.weights_of], i))
+        if lc.weights_of is not None:      # no part of its own: the running order below names the other layer's part once more
             continue
         p, m = f"l{i}", lc.mixer
         if lc.kind == "channel_delta":
@@ -58,7 +57,8 @@ def build_zepalorn(cfg: ZepalornConfig) -> ModelSpec:
         part_of[i] = len(layers)
         layers.append(SandwichBlock(LayerNorm(W, eps, f"{p}.norm1"), mixer, LayerNorm(W, eps, f"{p}.norm1b"),
                                     LayerNorm(W, eps, f"{p}.norm2") if ff else None, ff, LayerNorm(W, eps, f"{p}.norm2b") if ff else None))
-        schedule.append(LayerCall(part_of[i], i))
+    # layer i runs its own part, or the part of the layer whose weights it runs on, always with cache entry i
+    schedule = [LayerCall(part_of[i if lc.weights_of is None else lc.weights_of], i) for i, lc in enumerate(cfg.layers)]
     embedding = TokenEmbedding(cfg.vocab, W, "embed", scale=cfg.embedding_scale)
     return ModelSpec(
         config=cfg,

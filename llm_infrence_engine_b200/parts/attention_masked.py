@@ -39,8 +39,8 @@ class MaskedAttention(Mixer):
             raise ValueError("first tokens can only be kept where a window would pass them")
         if position is not None and position.dims > head_dim:
             raise ValueError(f"{position.dims} rotated dimensions do not fit heads of {head_dim}")
-        if conv_taps and not 2 <= conv_taps <= 8:
-            raise ValueError(f"a short convolution has 2 to 8 taps, got {conv_taps}")
+        if conv_taps and not 1 <= conv_taps <= 8:
+            raise ValueError(f"a short convolution has 1 to 8 taps, got {conv_taps}")
         self.hidden, self.num_heads, self.num_kv_heads = hidden, num_heads, num_kv_heads
         self.head_dim, self.v_head_dim, self.scale, self.prefix = head_dim, v_head_dim, float(scale), prefix
         self.position, self.interleaved = position, bool(interleaved)

@@ -37,8 +37,8 @@ class GatedDeltaMixer(Mixer):
                  random_rank: int = 16):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads cannot share {num_kv_heads} query/key heads")
-        if not 2 <= conv_taps <= 8:
-            raise ValueError(f"a short convolution has 2 to 8 taps, got {conv_taps}")
+        if not 1 <= conv_taps <= 8:
+            raise ValueError(f"a short convolution has 1 to 8 taps, got {conv_taps}")
         if head_dim > 256:
             raise ValueError(f"the delta rule's kernel keeps a column of the state in registers: head_dim {head_dim} is more than 256")
         self.hidden, self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim = hidden, num_heads, num_kv_heads, head_dim, v_head_dim
@@ -130,8 +130,8 @@ class StateSpaceMixer(Mixer):
         inner = num_heads * v_head_dim
         if inner % norm_groups:
             raise ValueError(f"{inner} channels cannot be normed in {norm_groups} equal parts")
-        if not 2 <= conv_taps <= 8:
-            raise ValueError(f"a short convolution has 2 to 8 taps, got {conv_taps}")
+        if not 1 <= conv_taps <= 8:
+            raise ValueError(f"a short convolution has 1 to 8 taps, got {conv_taps}")
         if state_size > 256:
             raise ValueError(f"the recurrence's kernel keeps a column of the state in registers: state size {state_size} is more than 256")
         self.hidden, self.num_heads, self.v_head_dim, self.state_size, self.groups = hidden, num_heads, v_head_dim, state_size, groups

@@ -12,8 +12,6 @@ from typing import Dict, List, Optional
 
 import torch
 
-SQRT_2_OVER_PI = math.sqrt(2.0 / math.pi)
-
 
 # ------------------------------------------------------------------------------------------------------------ small pieces
 def layer_norm(x, w, eps):
@@ -33,10 +31,6 @@ def silu(x):
 
 def softplus(x):
     return torch.where(x > 30, x, torch.log1p(torch.exp(torch.clamp(x, max=30))))
-
-
-def gelu_tanh(z):
-    return 0.5 * z * (1 + torch.tanh(SQRT_2_OVER_PI * (z + 0.044715 * z ** 3)))
 
 
 def causal_conv(u, w, bias=None):
@@ -207,7 +201,7 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, dtype=torch.
     """Logits [T, vocab] of one sequence (and, if asked, the residual stream after every layer run)."""
     W = {n: (t.to(dtype) if t.is_floating_point() else t) for n, t in weights.items()}
     eps = float(config["norm"]["eps"])
-    x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(config["embedding"]["scale"])
+    x = W["embed"][torch.as_tensor(tokens, dtype=torch.long)] * float(config.get("embedding", {}).get("scale", 1.0))
     after: List[torch.Tensor] = []
     for i, layer in enumerate(config["layers"]):
         p = f"l{layer.get('weights_of', i)}"

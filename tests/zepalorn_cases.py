@@ -129,6 +129,11 @@ def plain_logits(cfg, tensors, tokens):
 # ends in a norm that brings its result back to full size, so the rounding of a dozen sublayers adds up to a few per cent of the
 # logits' spread (measured 0.03 to 0.05 at these sizes); a wrong key or a lost state moves them by 0.3 and more
 LIMIT = {"float32": 3e-5, "bfloat16": 1e-1}
+
+# D: convolutions of a single tap (no state rows at all), and a first layer that runs on the weights of a LATER one
+_d_layers = [_ff(_delta(2, 1, 16, 8, 1), 24, 2.0), _ff(_parallel((2, 2, 8, 8, 0.3, 1, 7, 3.0, _rot(4, 20.0)), (2, 8, 8, 1, 2, 1)), 16, 1.5), _ff(_delta(2, 1, 16, 8, 1), 24, 2.0)]
+_d_layers[0]["weights_of"] = 2
+CASES["D"] = ({"architecture": "Zepalorn", "vocab": 40, "width": 24, "norm": {"eps": 1e-5}, "layers": _d_layers}, 8)
 LENS = {"a": 150, "b": 67, "c": 41, "d": 9, "e": 118, "f": 2}
 
 
