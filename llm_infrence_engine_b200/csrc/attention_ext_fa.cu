@@ -48,7 +48,8 @@ __device__ __forceinline__ uint32_t pack2(float a, float b) {
 }
 
 // KD: steps of 16 over the key entries (dk = 16 KD); NV: pairs of n8 tiles over the value entries (dv = 16 NV)
-template <int KD, int NV>
+// MASKS: kept first tokens, chunks and the soft cap are compiled in (else they are not looked at, and cost nothing)
+template <int KD, int NV, bool MASKS>
 __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int dk = 16 * KD, dv = 16 * NV, ks = dk + 8, vs = dv + 8;
@@ -77,9 +78,9 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
     int n0 = P.tile_info[2 * blockIdx.x], ntok = min(P.tile_info[2 * blockIdx.x + 1], tokens_per_tile);
     const int p_first = P.positions[n0], p_last = P.positions[n0 + ntok - 1];
     int lo = P.window > 0 ? max(0, p_first - P.window + 1) : 0;
-    if (P.ex.chunk > 0) lo = max(lo, (p_first / P.ex.chunk) * P.ex.chunk);
-    const int kept = min(P.ex.keep_first, lo);                               // keys [0, kept) are seen besides [lo, hi)
-    const int npre = (split == 0 && kept > 0) ? (kept + KEYS - 1) / KEYS : 0;   // their chunks come first, in the first slice
+    if (MASKS && P.ex.chunk > 0) lo = max(lo, (p_first / P.ex.chunk) * P.ex.chunk);
+    const int kept = MASKS ? min(P.ex.keep_first, lo) : 0;                   // keys [0, kept) are seen besides [lo, hi)
+    const int npre = (MASKS && split == 0 && kept > 0) ? (kept + KEYS - 1) / KEYS : 0;   // their chunks come first, in the first slice
     const int hi = p_last + 1;
     int per = (hi - lo + P.num_splits - 1) / P.num_splits;
     per = (per + KEYS - 1) / KEYS * KEYS;
@@ -98,7 +99,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
         row_head[i] = ok ? kvh * G + g : 0;
         row_g[i] = ok ? row % gh : 0;
         row_pos[i] = ok ? P.positions[n0 + t] : -1;
-        row_lo[i] = ok ? attn_ext::first_visible(row_pos[i], P.window, P.ex) : 0;
+        row_lo[i] = ok ? (MASKS ? attn_ext::first_visible(row_pos[i], P.window, P.ex) : (P.window > 0 ? max(0, row_pos[i] - P.window + 1) : 0)) : 0;
         float f = P.scale;
         if (P.ex.temp_every > 0 && ok) f = P.scale * (1.0f + P.ex.temp_coef * logf((float)((row_pos[i] + 1) / P.ex.temp_every + 1)));
         row_factor[i] = f;
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
                 for (int e = 0; e < 4; ++e) {
                     const int i = e >> 1;
                     float v = s[t][e] * row_factor[i];
-                    if (P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
+                    if (MASKS && P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
                     if (P.ex.rel) {
                         const int dist = row_pos[i] - (base + t * 8 + 2 * tig + (e & 1));
                         if (P.bias_in_smem) {
@@ -214,11 +215,11 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
                     const int i = e >> 1;
                     const int key = base + t * 8 + 2 * tig + (e & 1);
                     const int p = row_pos[i];
-                    const bool seen = key <= p && key < range_hi && key >= range_lo && (key >= row_lo[i] || key < P.ex.keep_first);
+                    const bool seen = key <= p && key < range_hi && key >= range_lo && (key >= row_lo[i] || (MASKS && key < P.ex.keep_first));
                     float v = -INFINITY;
                     if (seen) {
                         v = s[t][e] * row_factor[i];
-                        if (P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
+                        if (MASKS && P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
                         if (P.ex.rel) {
                             const int dist = p - key;
                             if (P.bias_in_smem) {
@@ -323,14 +324,20 @@ __global__ void __launch_bounds__(THREADS) attn_ext_fa_kernel(const Params P) {
 size_t smem_bytes(int dk, int dv) { return 2 * ((size_t)ROWS * (dk + 8) + 2 * KEYS * (dk + 8) + 2 * KEYS * (dv + 8)); }
 size_t bias_bytes(int rel_rows, int gh, int n_rows_of) { return sizeof(float) * (size_t)rel_rows * gh + 2 * (size_t)((n_rows_of + 1) & ~1); }
 
-template <int KD, int NV>
-int launch(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
+template <int KD, int NV, bool MASKS>
+int launch_as(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
     static bool set = false;
     if (!set) {
-        cudaFuncSetAttribute(attn_ext_fa_kernel<KD, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(attn_ext_fa_kernel<KD, NV, MASKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         set = true;
     }
-    return launch_kernel(attn_ext_fa_kernel<KD, NV>, grid, dim3(THREADS), smem, s, P);
+    return launch_kernel(attn_ext_fa_kernel<KD, NV, MASKS>, grid, dim3(THREADS), smem, s, P);
+}
+
+template <int KD, int NV>
+int launch(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
+    if (P.ex.keep_first > 0 || P.ex.chunk > 0 || P.ex.softcap > 0.f) return launch_as<KD, NV, true>(P, grid, smem, s);
+    return launch_as<KD, NV, false>(P, grid, smem, s);
 }
 
 }  // namespace

@@ -56,7 +56,8 @@ __device__ __forceinline__ void bar_rows(int id) { asm volatile("bar.sync %0, 12
 // NT: n8 tiles of a part's value columns (dv = 32 * NT). R: row blocks of 16 rows per warp: a tile has 32 * R rows, and a warp
 // (rb, part) works on the row blocks rb * R .. rb * R + R - 1, so a chunk's keys and values are fetched and read from shared
 // memory once for R times the rows (prompt portions; decoded tokens take R = 1).
-template <int NT, int R, int ST>
+// MASKS: kept first tokens, chunks and the soft cap are compiled in (else they are not looked at, and cost nothing)
+template <int NT, int R, int ST, bool MASKS>
 __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int ROWS_T = ROWS * R;
@@ -95,9 +96,9 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
     ntok = min(ntok, tokens_per_tile);
     const int p_first = P.positions[n0], p_last = P.positions[n0 + ntok - 1];
     int lo = P.window > 0 ? max(0, p_first - P.window + 1) : 0;
-    if (P.ex.chunk > 0) lo = max(lo, (p_first / P.ex.chunk) * P.ex.chunk);
-    const int kept = min(P.ex.keep_first, lo);                               // keys [0, kept) are seen besides [lo, hi)
-    const int npre = (split == 0 && kept > 0) ? (kept + KEYS - 1) / KEYS : 0;   // their chunks come first, in the first slice
+    if (MASKS && P.ex.chunk > 0) lo = max(lo, (p_first / P.ex.chunk) * P.ex.chunk);
+    const int kept = MASKS ? min(P.ex.keep_first, lo) : 0;                   // keys [0, kept) are seen besides [lo, hi)
+    const int npre = (MASKS && split == 0 && kept > 0) ? (kept + KEYS - 1) / KEYS : 0;   // their chunks come first, in the first slice
     const int hi = p_last + 1;
     int per = (hi - lo + P.num_splits - 1) / P.num_splits;
     per = (per + KEYS - 1) / KEYS * KEYS;
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
             row_head[r][i] = ok ? kvh * G + g : 0;
             row_g[r][i] = ok ? row % gh : 0;
             row_pos[r][i] = ok ? P.positions[n0 + t] : -1;
-            row_lo[r][i] = ok ? attn_ext::first_visible(row_pos[r][i], P.window, P.ex) : 0;
+            row_lo[r][i] = ok ? (MASKS ? attn_ext::first_visible(row_pos[r][i], P.window, P.ex) : (P.window > 0 ? max(0, row_pos[r][i] - P.window + 1) : 0)) : 0;
             float f = P.scale;
             if (P.ex.temp_every > 0 && ok) f = P.scale * (1.0f + P.ex.temp_coef * logf((float)((row_pos[r][i] + 1) / P.ex.temp_every + 1)));
             row_factor[r][i] = f;
@@ -249,11 +250,11 @@ __global__ void __launch_bounds__(THREADS) attn_ext_mma_kernel(const Params P) {
                     const int i = e >> 1;
                     const int key = base + part * 16 + t * 8 + 2 * tig + (e & 1);
                     const int p = row_pos[r][i];
-                    const bool seen = key <= p && key < range_hi && key >= range_lo && (key >= row_lo[r][i] || key < P.ex.keep_first);
+                    const bool seen = key <= p && key < range_hi && key >= range_lo && (key >= row_lo[r][i] || (MASKS && key < P.ex.keep_first));
                     float v = -INFINITY;
                     if (seen) {
                         v = (s[r][t][e] + s2[r][t][e]) * row_factor[r][i];
-                        if (P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
+                        if (MASKS && P.ex.softcap > 0.f) v = P.ex.softcap * tanhf(v / P.ex.softcap);
                         if (P.ex.rel) {
                             const int dist = p - key;
                             if (P.bias_in_smem) {
@@ -411,14 +412,20 @@ size_t bias_bytes(int rel_rows, int gh, int n_rows_of) { return sizeof(float) * 
 
 constexpr int DEEP = 4;   // stages of the ring for decoded tokens, where shared memory has room for them
 
-template <int NT, int R, int ST>
-int launch_st(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
+template <int NT, int R, int ST, bool MASKS>
+int launch_st_as(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
     static bool set = false;
     if (!set) {
-        cudaFuncSetAttribute(attn_ext_mma_kernel<NT, R, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        cudaFuncSetAttribute(attn_ext_mma_kernel<NT, R, ST, MASKS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         set = true;
     }
-    return launch_kernel(attn_ext_mma_kernel<NT, R, ST>, grid, dim3(THREADS), smem, s, P);
+    return launch_kernel(attn_ext_mma_kernel<NT, R, ST, MASKS>, grid, dim3(THREADS), smem, s, P);
+}
+
+template <int NT, int R, int ST>
+int launch_st(const Params& P, dim3 grid, size_t smem, cudaStream_t s) {
+    if (P.ex.keep_first > 0 || P.ex.chunk > 0 || P.ex.softcap > 0.f) return launch_st_as<NT, R, ST, true>(P, grid, smem, s);
+    return launch_st_as<NT, R, ST, false>(P, grid, smem, s);
 }
 
 template <int NT, int R>
