@@ -133,6 +133,13 @@ LIMIT = {"float32": 3e-5, "bfloat16": 1e-1}
 # D: convolutions of a single tap (no state rows at all), and a first layer that runs on the weights of a LATER one
 _d_layers = [_ff(_delta(2, 1, 16, 8, 1), 24, 2.0), _ff(_parallel((2, 2, 8, 8, 0.3, 1, 7, 3.0, _rot(4, 20.0)), (2, 8, 8, 1, 2, 1)), 16, 1.5), _ff(_delta(2, 1, 16, 8, 1), 24, 2.0)]
 _d_layers[0]["weights_of"] = 2
+# E: sizes that take the kernels' slow paths: a width that is no multiple of 8, heads of 20 and 10 entries (no 16-byte pieces), values
+# of 12, 6 and 4, more kept tokens than the window is long, chunks of 3, convolutions of 8, 5 and 6 taps, a state of 12, pages of 4
+CASES["E"] = (_model(57, 44, 1e-6, 2.0, [
+    _ff(_delta(3, 1, 10, 6, 8), 52, 0.5),
+    _ff(_attention(2, 2, 20, 12, 0.22, window=7, keep_first=9, rot=_rot(6, 7.0, (1.5, 24, 3.0, 0.5))), None),
+    _ff(_parallel((3, 1, 12, 20, 0.3, 5, 3, 1.0, _rot(12, 40.0)), (5, 4, 12, 5, 5, 6)), 36, 4.0),
+], again=(0,)), 4)
 CASES["D"] = ({"architecture": "Zepalorn", "vocab": 40, "width": 24, "norm": {"eps": 1e-5}, "layers": _d_layers}, 8)
 LENS = {"a": 150, "b": 67, "c": 41, "d": 9, "e": 118, "f": 2}
 
