@@ -20,6 +20,9 @@ batch of 8 requests and a context of 8192 tokens. A "step" is one decode step of
 ``roofline``  bytes a decode step must read (every weight once + the live requests' cache) / its time.
 ``points``    decode tokens per second at batch 1 and 64, same method as ``value``.
 
+``--workload serving | luvutar | zepalorn`` measure other things (a stream of requests through the engine; the two other architectures
+beside Qwen2 of equal size, with ``--kernels`` also kernel by kernel) and print lines of their own; the default line is unchanged by them.
+
 Peaks come from MEASURED_PEAKS.json beside this file when it exists, else 6.65 TB/s and 1.59 PFLOP/s.
 More than one GPU is outside this engine: ``--gpus N`` with N > 1 prints one line and exits with 2.
 """
@@ -990,8 +993,8 @@ def main() -> int:
     ap.add_argument("--only", default="all", choices=["all", "decode", "prefill"], help="measure one part only (for profiling); the JSON line then lacks the rest")
     ap.add_argument("--workload", default="steps", choices=["steps", "serving", "luvutar", "zepalorn"],
                     help="serving: continuous batching of --requests requests (prompts U[128,2048], outputs U[64,512]) through Engine; "
-                         "luvutar: the Luvutar decoder at two layer sizes beside the Qwen2 decoder of equal size (decode and prefill)")
-    ap.add_argument("--kernels", action="store_true", help="luvutar: also time its kernels one by one beside their Qwen2 counterparts")
+                         "luvutar, zepalorn: that decoder at two layer sizes beside the Qwen2 decoder of equal size (decode and prefill)")
+    ap.add_argument("--kernels", action="store_true", help="luvutar, zepalorn: also time its kernels one by one beside their Qwen2 counterparts")
     ap.add_argument("--requests", type=int, default=64)
     ap.add_argument("--token-budget", type=int, default=2048, help="serving: tokens per step (max_num_batched_tokens)")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS, help="length of the timed prompt")
