@@ -6,8 +6,7 @@ from typing import Dict, Optional, Sequence
 import torch
 
 from ..cache.spec import FixedStateSpec
-from .base import (ANY, INIT_LOG_RATE, INIT_NORM, INIT_NORMAL, INIT_PROJ, INIT_SMALL, INIT_STEP_BIAS, INIT_TAPS, MATRIX, VECTOR, Mixer, ParamSpec,
-                   Part, Source)
+from .base import ANY, INIT_LOG_RATE, INIT_NORM, INIT_PROJ, INIT_SMALL, INIT_STEP_BIAS, INIT_TAPS, MATRIX, VECTOR, Mixer, ParamSpec, Part, Source
 
 
 def _padded(w: torch.Tensor, multiple: int = 8) -> torch.Tensor:

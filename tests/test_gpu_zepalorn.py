@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from torch_kernels import TorchKernels
-from zepalorn_cases import (CASES, LIMIT, check_long_decoding, check_mixed, check_whole_and_cut, cuts_of, load_plain, make_folder, plain_logits, prompt,
+from zepalorn_cases import (CASES, check_long_decoding, check_mixed, check_whole_and_cut, cuts_of, load_plain, make_folder, plain_logits, prompt,
                             replayer, row_error, run_alone, setup_case)
 
 pytestmark = pytest.mark.gpu

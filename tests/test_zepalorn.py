@@ -9,8 +9,7 @@ import torch
 
 import plain_zepalorn as plain
 from torch_kernels import TorchKernels
-from zepalorn_cases import (CASES, LIMIT, check_long_decoding, check_mixed, check_whole_and_cut, load_plain, make_folder, plain_logits, prompt,
-                            row_error, setup_case)
+from zepalorn_cases import CASES, check_long_decoding, check_mixed, check_whole_and_cut, plain_logits, setup_case
 
 
 @pytest.fixture(scope="module")
